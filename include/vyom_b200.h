@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define VY_ABI_VERSION 9
+#define VY_ABI_VERSION 10
 
 #if defined(__GNUC__)
 #define VY_API __attribute__((visibility("default")))
@@ -822,9 +822,13 @@ typedef struct VyRopeSplit {
 } VyRopeSplit;
 VY_API int vy_rope_split(const VyRopeSplit* p);
 
-/* Router of a mixture of experts: score = sigmoid(logits[row, e]) (fp32 logits), the `top` largest (ties: lowest index),
- * weight = score / (sum of the chosen scores + 1e-20) * scale. Writes idx [rows, top] int32 and weight [rows, top] fp32
- * (largest first) and, when `dense` is given, dense[row, e] = weight or 0 ([rows, experts] fp32). experts <= 1024. */
+/* Router of a mixture of experts over fp32 logits. score = sigmoid(logits[row, e]) (kind VY_ROUTE_SIGMOID) or the softmax over
+ * all experts (VY_ROUTE_SOFTMAX). With groups > 1 the experts form `groups` equal runs of neighbours, a run scores as its best
+ * member and only members of the `keep_groups` best runs are eligible. The `top` largest eligible scores are chosen (ties: lowest
+ * index). weight = score / (sum of the chosen scores + 1e-20) * scale, or score * scale when raw_weights is set. Writes idx
+ * [rows, top] int32 and weight [rows, top] fp32 (largest first) and, when `dense` is given, dense[row, e] = weight or 0
+ * ([rows, experts] fp32). experts <= 1024; groups must divide experts; top <= keep_groups * experts / groups. */
+enum { VY_ROUTE_SIGMOID = 0, VY_ROUTE_SOFTMAX = 1 };
 typedef struct VyMoeRoute {
   int64_t rows; int32_t experts, top;
   const float* logits; int64_t ld_logits;
@@ -832,6 +836,7 @@ typedef struct VyMoeRoute {
   int32_t* idx; float* weight;
   float* dense;
   void* stream;
+  int32_t kind, groups, keep_groups, raw_weights; /* 0, 0, 0, 0: sigmoid scores, no groups, normalised weights */
 } VyMoeRoute;
 VY_API int vy_moe_route(const VyMoeRoute* p);
 
@@ -879,6 +884,99 @@ typedef struct VyMoeCombine {
   void* stream;
 } VyMoeCombine;
 VY_API int vy_moe_combine(const VyMoeCombine* p);
+
+/* Gated experts: hidden activations of all experts at once, h [rows, experts * 2 ff + 2 shared_ff], expert e's block being
+ * [gate (ff) | up (ff)], the shared expert's [gate (shared_ff) | up (shared_ff)] last:
+ *   g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1)        (fp32)
+ *   out[row, e * ff + j] = y * dense[row * ld_dense + e] (dense null = 1; a zero weight writes 0 without reading h);
+ *   out[row, experts * ff + j] = y of the shared block with shared_limit (weight 1).
+ * limit <= 0 = no clamp. experts or shared_ff may be 0. */
+typedef struct VyMoeGlu {
+  int64_t rows; int32_t experts, ff, shared_ff;
+  const void* h; int64_t ldh; int32_t h_dtype;
+  const float* dense; int64_t ld_dense;
+  float limit, shared_limit, alpha;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyMoeGlu;
+VY_API int vy_moe_glu(const VyMoeGlu* p);
+
+/* Layer norm of packed rows with fp32 statistics: out[t, c] = (x[st, c] - mean) / sqrt(var + eps) * weight[c] + bias[c], var the
+ * mean squared deviation, st = row_index ? row_index[t] : t. weight / bias may be null (1 / 0). */
+typedef struct VyLayerNorm {
+  int64_t tokens; int32_t width;
+  const int32_t* row_index;
+  const void* x; int64_t ldx; int32_t x_dtype;
+  const void* weight; const void* bias; int32_t w_dtype;
+  float eps;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyLayerNorm;
+VY_API int vy_layer_norm(const VyLayerNorm* p);
+
+/* Closes a layer whose sublayers ran side by side on one normed input, all in fp32:
+ *   r[t, c] = x[t, c] + gate1 * y1[t, c] + gate2 * y2[t, c],   gate_i = g_i ? sigmoid(g_i[t, c]) : 1   (y2 null = no second sublayer)
+ * and, with `stack` (fp32 [depth, rows, width], slices `stack_stride` elements apart): r is stored as slice depth - 1 and
+ *   mixed[t, c] = sum_j coef[j] * stack[j][t, c], j = 0 .. depth - 1 (coef fp32 [depth]);  without a stack mixed = r.
+ * mixed goes to `mixed` (fp32, may alias x) and, when norm_out is given, its layer norm (norm_weight, norm_bias, eps as in
+ * vy_layer_norm) to norm_out: the input of the next layer's products. */
+typedef struct VyDepthMix {
+  int64_t rows; int32_t width;
+  const float* x; int64_t ldx;
+  const void* y1; int64_t ld_y1; int32_t y1_dtype; const void* g1; int64_t ld_g1; int32_t g1_dtype;
+  const void* y2; int64_t ld_y2; int32_t y2_dtype; const void* g2; int64_t ld_g2; int32_t g2_dtype;
+  float* stack; int64_t stack_stride; int32_t depth; const float* coef;
+  float* mixed; int64_t ld_mixed;
+  const void* norm_weight; const void* norm_bias; int32_t norm_w_dtype; float eps;
+  void* norm_out; int64_t ld_norm_out; int32_t norm_out_dtype;
+  void* stream;
+} VyDepthMix;
+VY_API int vy_depth_mix(const VyDepthMix* p);
+
+/* Rotates the query and key heads of a packed projection by position and stores the step's keys and values in their pages, one
+ * launch: q [rows, heads * dim] is rotated in place; k [rows, kv_heads * dim] is rotated into k_pool and v [rows, kv_heads * vdim]
+ * copied into v_pool at each token's page row (pools as in vy_kv_page_write). Entries (2i, 2i + 1), i < rot_dims / 2, of every
+ * head turn by pos * inv_freq[i]; the rest pass. q / k / v share a dtype (fp32 for in-place rotation at full precision). */
+typedef struct VyRopeKvWrite {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0;
+  const int32_t* block_table; int32_t table_width, block_size;
+  void* q; int64_t ldq; const void* k; int64_t ldk; const void* v; int64_t ldv; int32_t in_dtype;
+  int32_t heads, kv_heads, dim, vdim, rot_dims;
+  const float* inv_freq;
+  void* k_pool; void* v_pool; int32_t pool_dtype;
+  void* stream;
+} VyRopeKvWrite;
+VY_API int vy_rope_kv_write(const VyRopeKvWrite* p);
+
+/* Attention whose query heads exchange scores before the softmax, over the paged pools (which already hold the step's keys):
+ *   s_h[i, j] = (q_h[i] . k_g(h)[j]) * scale;  softcap > 0: s <- softcap * tanh(s / softcap);
+ *   talk ([heads, heads], row = receiving head): s_h <- sum_b talk[h, b] * s_b   (null = no exchange);
+ *   query i sees key j iff j <= i and (window <= 0 or i - j < window);
+ *   weights = exp(s_j) / (sink term + sum_j exp(s_j)), sink term = exp(sink[h]) with `sink`, 1 with zero_sink, else 0;
+ *   out[i, h * vdim + c] = sum_j weight_j v_g(h)[j, c] * (gate ? sigmoid(gate[i, gate_per_channel ? h * vdim + c : h]) : 1).
+ * Scores, the exchange, the softmax and the sums are fp32. Because every head's weights depend on all heads' scores, one CTA
+ * owns ALL heads of its queries: a register-tiled form (rows = heads x queries) for prompts, a form with one query per CTA and
+ * the keys split over CTAs (merged from `workspace`) for single tokens and short portions. heads <= 1024. */
+typedef struct VyTalkAttn {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0;
+  const int32_t* block_table; int32_t table_width, block_size;
+  const void* q; int64_t ldq; int32_t q_dtype;
+  const void* k_pool; const void* v_pool; int32_t pool_dtype;
+  int32_t heads, kv_heads, dim, vdim;
+  float scale, softcap;
+  int32_t window;
+  const void* talk; int32_t talk_dtype;
+  const void* sink; int32_t sink_dtype; int32_t zero_sink;
+  const void* gate; int64_t ld_gate; int32_t gate_dtype; int32_t gate_per_channel;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  float* workspace; int64_t workspace_floats; /* vy_talk_attn_workspace_floats(...) floats, or null when that is 0 */
+  int32_t force_form; /* 0 = chosen by the step's shape; 1 = one query per CTA; 2 = tiled (an error if the sizes do not fit it) */
+  void* stream;
+} VyTalkAttn;
+VY_API int64_t vy_talk_attn_workspace_floats(int32_t n_seqs, int32_t max_new, int32_t table_width, int32_t block_size, int32_t heads, int32_t vdim);
+VY_API int vy_talk_attn(const VyTalkAttn* p);
 
 /* vy_patchify — NCHW pixels -> [B * (H/ph) * (W/pw), C*ph*pw] patch rows, (c, i, j) order with j
  * fastest: the im2col of the stride==kernel nn.Conv2d at VyomAI/models/vision_encoder.py:83-88,114

@@ -18,4 +18,5 @@ from .paged import ContinuousBatchEngine, PagedKVManager, SequenceState  # noqa:
 from .paged import HybridBatchEngine, HybridCacheManager, HybridSequence  # noqa: F401  (packed steps over pages + state slots)
 from .models.gelutar import GelutarConfig, GelutarForCausalLM  # noqa: F401
 from .models.zugunex import ZugunexConfig, ZugunexForCausalLM  # noqa: F401
+from .models.vazepel import VazepelConfig, VazepelForCausalLM  # noqa: F401
 from .registry import load_model, register_model  # noqa: F401

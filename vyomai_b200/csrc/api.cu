@@ -209,6 +209,11 @@ int vy_abi_sizeof(const char* name) {
   VY_SZ(VyRopeSplit);
   VY_SZ(VyMoeRoute);
   VY_SZ(VyMoeScale);
+  VY_SZ(VyMoeGlu);
+  VY_SZ(VyLayerNorm);
+  VY_SZ(VyDepthMix);
+  VY_SZ(VyRopeKvWrite);
+  VY_SZ(VyTalkAttn);
   VY_SZ(VyMoeSort);
   VY_SZ(VyMoeGather);
   VY_SZ(VyMoeCombine);

@@ -114,11 +114,23 @@ struct RouteDev {
   const float* logits; long long ld;
   float scale;
   int* idx; float* weight; float* dense;
+  int kind, groups, keep_groups, raw;
 };
 
 constexpr int ROUTE_WARPS = 4;
 
-// one warp per row: scores in shared memory, `top` rounds of (max value, lowest index)
+// (value, index) maximum over a warp, ties to the lowest index
+__device__ __forceinline__ void warp_argmax(float& bv, int& bi) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+}
+
+// one warp per row: scores in shared memory (sigmoid, or softmax over all experts), members of the groups that were not kept
+// struck out, then `top` rounds of (max value, lowest index)
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(RouteDev d) {
   pdl_trigger();
   pdl_wait();
@@ -126,12 +138,44 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(RouteDev d)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long r = static_cast<long long>(blockIdx.x) * ROUTE_WARPS + warp;
   if (r >= d.rows) return;
-  float* sc = route_smem + warp * d.experts;
+  float* sc = route_smem + warp * (d.experts + d.groups);
+  float zmax = -INFINITY, zsum = 0.f;
+  if (d.kind == VY_ROUTE_SOFTMAX) {
+    for (int e = lane; e < d.experts; e += 32) zmax = fmaxf(zmax, d.logits[r * d.ld + e]);
+    zmax = warp_max(zmax);
+    for (int e = lane; e < d.experts; e += 32) zsum += expf(d.logits[r * d.ld + e] - zmax);
+    zsum = warp_sum(zsum);
+  }
   for (int e = lane; e < d.experts; e += 32) {
-    sc[e] = sigmoidf_(d.logits[r * d.ld + e]);
+    const float z = d.logits[r * d.ld + e];
+    sc[e] = d.kind == VY_ROUTE_SOFTMAX ? expf(z - zmax) / zsum : sigmoidf_(z);
     if (d.dense) d.dense[r * d.experts + e] = 0.f;
   }
   __syncwarp();
+  if (d.groups > 1) {
+    float* gs = sc + d.experts;   // a group's score: its best member; -inf once the group is kept
+    const int per = d.experts / d.groups;
+    for (int g = lane; g < d.groups; g += 32) {
+      float b = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, sc[e]);
+      gs[g] = b;
+    }
+    __syncwarp();
+    for (int k = 0; k < d.keep_groups; ++k) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < d.groups; g += 32) {
+        const float v = gs[g];
+        if (v > bv || (v == bv && v != -INFINITY && g < bi)) { bv = v; bi = g; }
+      }
+      warp_argmax(bv, bi);
+      if (lane == 0 && bi < d.groups) gs[bi] = -INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < d.experts; e += 32)
+      if (gs[e / per] != -INFINITY) sc[e] = -INFINITY;   // scores are positive, so a kept group never reads -inf here by itself
+    __syncwarp();
+  }
   float sum = 0.f;
   float my_val = 0.f;   // lane k keeps the k-th choice (top <= 32 per pass; larger tops loop)
   int my_idx = 0;
@@ -142,12 +186,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(RouteDev d)
       const float v = sc[e];
       if (v > bv) { bv = v; bi = e; }   // ascending e: the lowest index of equal values stays
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
+    warp_argmax(bv, bi);
     sum += bv;
     if (lane == (k & 31)) { my_val = bv; my_idx = bi; }
     if (lane == 0) sc[bi] = -INFINITY;
@@ -162,7 +201,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(RouteDev d)
     }
   }
   __syncwarp();
-  const float norm = d.scale / (sum + 1e-20f);
+  const float norm = d.raw ? d.scale : d.scale / (sum + 1e-20f);
   for (int k = lane; k < d.top; k += 32) {
     const float w = d.weight[r * d.top + k] * norm;
     d.weight[r * d.top + k] = w;
@@ -375,10 +414,17 @@ extern "C" int vy_moe_route(const VyMoeRoute* p) {
   d.rows = p->rows; d.experts = p->experts; d.top = p->top;
   d.logits = p->logits; d.ld = p->ld_logits; d.scale = p->scale;
   d.idx = p->idx; d.weight = p->weight; d.dense = p->dense;
+  d.kind = p->kind; d.raw = p->raw_weights;
+  d.groups = p->groups > 1 ? p->groups : 0; d.keep_groups = d.groups ? p->keep_groups : 0;
+  VY_CHECK_ARG(p->kind == VY_ROUTE_SIGMOID || p->kind == VY_ROUTE_SOFTMAX, "vy_moe_route: unknown kind %d", p->kind);
+  VY_CHECK_ARG(d.groups == 0 || (p->experts % d.groups == 0 && d.keep_groups > 0 && d.keep_groups <= d.groups &&
+                                 p->top <= d.keep_groups * (p->experts / d.groups)),
+               "vy_moe_route: %d groups must divide %d experts, keep %d of them, top %d within the kept groups", p->groups, p->experts,
+               p->keep_groups, p->top);
   const long long blocks = (p->rows + ROUTE_WARPS - 1) / ROUTE_WARPS;
   VY_CHECK_ARG(blocks <= 2147483647LL, "vy_moe_route: too many rows");
   VY_CUDA_OK(launch_kernel(moe_route_kernel, dim3(static_cast<unsigned>(blocks)), dim3(ROUTE_WARPS * 32),
-                           sizeof(float) * ROUTE_WARPS * p->experts, static_cast<cudaStream_t>(p->stream), d));
+                           sizeof(float) * ROUTE_WARPS * (p->experts + d.groups), static_cast<cudaStream_t>(p->stream), d));
   VY_LAUNCH_OK();
   count_launch();
   return VY_OK;

@@ -15,81 +15,6 @@
 
 namespace vy {
 
-__device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc) {
-  acc = fmaf(a.x, b.x, acc);
-  acc = fmaf(a.y, b.y, acc);
-  acc = fmaf(a.z, b.z, acc);
-  return fmaf(a.w, b.w, acc);
-}
-__device__ __forceinline__ void axpy4(float (&acc)[4], const float a, const float4 x) {
-  acc[0] = fmaf(a, x.x, acc[0]);
-  acc[1] = fmaf(a, x.y, acc[1]);
-  acc[2] = fmaf(a, x.z, acc[2]);
-  acc[3] = fmaf(a, x.w, acc[3]);
-}
-__device__ __forceinline__ const float4& f4(const float* p) { return *reinterpret_cast<const float4*>(p); }
-
-// Rows [0, rows) of a [rows, width] block of `src` into shared memory (row stride ld, zero-filled up to width4 columns, `act`
-// applied): row j starts at element off(j) of src, or is all zero when off(j) < 0. Global loads go out in batches of 8 per
-// thread before any of them is used, so a tile costs about one memory round trip. vec: src is fp32 and every row start and the
-// width are multiples of 4 elements (16-byte loads).
-template <int T, typename OffFn>
-__device__ __forceinline__ void rows_to_smem(float* dst, int ld, int rows, int width, int width4, const void* src, int dt, bool vec, int act,
-                                             OffFn off) {
-  constexpr int U = 8;
-  if (vec) {
-    const int w4 = width4 >> 2, total = rows * w4;
-    for (int e0 = threadIdx.x; e0 < total; e0 += T * U) {
-      float4 v[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int e = e0 + u * T;
-        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (e < total) {
-          const int j = e / w4, c = (e - j * w4) << 2;
-          const long long o = off(j);
-          if (o >= 0 && c < width) v[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + o + c);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int e = e0 + u * T;
-        if (e < total) {
-          const int j = e / w4, c = (e - j * w4) << 2;
-          if (act != VY_UACT_NONE) {
-            v[u].x = apply_uact(v[u].x, act); v[u].y = apply_uact(v[u].y, act);
-            v[u].z = apply_uact(v[u].z, act); v[u].w = apply_uact(v[u].w, act);
-          }
-          *reinterpret_cast<float4*>(dst + j * ld + c) = v[u];
-        }
-      }
-    }
-  } else {
-    const int total = rows * width4;
-    for (int e0 = threadIdx.x; e0 < total; e0 += T * U) {
-      float v[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int e = e0 + u * T;
-        v[u] = 0.f;
-        if (e < total) {
-          const int j = e / width4, c = e - j * width4;
-          const long long o = off(j);
-          if (o >= 0 && c < width) v[u] = ld_as_float(src, dt, o + c);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int e = e0 + u * T;
-        if (e < total) {
-          const int j = e / width4, c = e - j * width4;
-          dst[j * ld + c] = act != VY_UACT_NONE ? apply_uact(v[u], act) : v[u];
-        }
-      }
-    }
-  }
-}
-
 // ---- chunked linear attention ------------------------------------------------------------------------------------------
 constexpr int LA_C = 64;    // tokens per chunk
 constexpr int LA_T = 256;   // threads: a 16 x 16 grid; thread (ti, tj) owns rows ti + 16 r and VS / 16 adjacent value columns

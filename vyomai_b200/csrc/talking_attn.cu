@@ -1,0 +1,546 @@
+// Attention whose query heads exchange scores before the softmax ("talking heads"), over pages, in fp32:
+//   s_h = cap(q_h . k_g(h) * scale),  s_h <- sum_b talk[h, b] s_b,  causal (optionally windowed) mask,
+//   softmax with an optional extra term in the denominator (a learned per-head sink, or a sink of score 0),
+//   o_h = sum_j w_h[j] v_g(h)[j], times an optional sigmoid gate per head or per channel.
+// A head's weights depend on every head's scores of the same (query, key) pair, so a CTA owns ALL heads of its queries:
+//   * rows form: one query token per CTA (and one split of its keys). Per tile of 64 keys, for each key/value head the key rows
+//     are staged in shared memory once and every query head of the group is contracted with them; the [heads, 64] score block
+//     is mixed through `talk` in shared memory, the softmax is online per head, and the value rows are staged and
+//     accumulated the same way. Splits write (max, sum, unnormalised output) per head and a merge kernel combines them:
+//     single tokens with long contexts fill the GPU although each token is one row.
+//   * tiled form (prompts): rows = (head, query) pairs of a tile of TQ queries, 64 or 128 rows by 32 (or 16) keys on a 16 x 16
+//     thread grid with register tiles; the key rows of ALL key/value heads are staged per tile, so every thread contracts its
+//     rows at once, and the same exchange runs in shared memory between the two contractions.
+// Both forms give the same values up to fp32 rounding, whatever the portion sizes.
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+
+#include "seqmix.cuh"
+
+namespace vy {
+
+struct TalkDev {
+  const int* cu; const int* pos0; const int* table; int tw, bs;
+  const void* q; long long ldq; int q_dt;
+  const void* kp; const void* vp; int pool_dt;
+  int heads, kv_heads, dim, vdim;
+  float scale, softcap; int window;
+  const void* talk; int talk_dt;
+  const void* sink; int sink_dt; int zero_sink;
+  const void* gate; long long ld_gate; int gate_dt; int gate_ch;
+  void* out; long long ld_out; int out_dt;
+};
+
+__device__ __forceinline__ float cap_score(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+
+// the extra softmax term of head h as (score, present)
+__device__ __forceinline__ bool sink_of(const TalkDev& d, int h, float& s) {
+  if (d.sink) { s = ld_as_float(d.sink, d.sink_dt, h); return true; }
+  s = 0.f;
+  return d.zero_sink != 0;
+}
+
+__device__ __forceinline__ float gate_of(const TalkDev& d, long long row, int h, int c) {
+  if (!d.gate) return 1.f;
+  return sigmoidf_(ld_as_float(d.gate, d.gate_dt, row * d.ld_gate + (d.gate_ch ? static_cast<long long>(h) * d.vdim + c : h)));
+}
+
+// ---- rows form ------------------------------------------------------------------------------------------------------------------
+constexpr int TR_T = 256;   // threads
+constexpr int TR_N = 64;    // keys per tile
+
+// grid (token of the sequence, sequence, split). Shared memory (floats): q [H][dim4] | staged rows [TR_N][ld_s] | S [H][TR_N] |
+// P [H][TR_N] | talk [H][H] | m, l, corr [H] each | acc [H][vdim] | key rows (int) [TR_N].
+__global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim4, int vdim4, int ld_s, bool qvec, bool kvvec, int splits, float* ws) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float tr_smem[];
+  const int H = d.heads, G = d.kv_heads, per = H / G;
+  float* q_s = tr_smem;
+  float* kv_s = q_s + H * dim4;
+  float* S_s = kv_s + TR_N * ld_s;
+  float* P_s = S_s + H * TR_N;
+  float* T_s = P_s + H * TR_N;
+  float* m_s = T_s + H * H;
+  float* l_s = m_s + H;
+  float* c_s = l_s + H;
+  float* acc_s = c_s + H;
+  int* krow_s = reinterpret_cast<int*>(acc_s + H * d.vdim);
+  const int s = blockIdx.y, i = blockIdx.x, split = blockIdx.z;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int base = d.cu[s], n = d.cu[s + 1] - base;
+  if (i >= n) return;
+  const long long qrow = base + i;
+  const int p = d.pos0[s] + i;
+  const int lo = d.window > 0 ? max(p - d.window + 1, 0) : 0;
+  const int count = p - lo + 1;
+  const int tiles = (count + TR_N - 1) / TR_N;
+  const int tps = (tiles + splits - 1) / splits;
+  const int tile0 = split * tps, tile1 = min(tiles, tile0 + tps);
+  const int* tab = d.table + static_cast<long long>(s) * d.tw;
+
+  rows_to_smem<TR_T>(q_s, dim4, H, d.dim, dim4, d.q, d.q_dt, qvec, VY_UACT_NONE,
+                     [&](int h) { return qrow * d.ldq + static_cast<long long>(h) * d.dim; });
+  for (int e = t; e < H * H; e += TR_T) T_s[e] = d.talk ? ld_as_float(d.talk, d.talk_dt, e) : (e / H == e % H ? 1.f : 0.f);
+  for (int h = t; h < H; h += TR_T) {
+    float sk;
+    const bool has = splits == 1 && sink_of(d, h, sk);   // with splits the merge adds the sink
+    m_s[h] = has ? sk : -INFINITY;
+    l_s[h] = has ? 1.f : 0.f;
+  }
+  for (int e = t; e < H * d.vdim; e += TR_T) acc_s[e] = 0.f;
+
+  for (int tile = tile0; tile < tile1; ++tile) {
+    const int c0 = tile * TR_N;
+    const int nk = min(TR_N, count - c0);
+    __syncthreads();
+    if (t < TR_N) {
+      const int kp = lo + c0 + t;
+      krow_s[t] = t < nk ? tab[kp / d.bs] * d.bs + kp % d.bs : -1;
+    }
+    for (int g = 0; g < G; ++g) {
+      __syncthreads();
+      rows_to_smem<TR_T>(kv_s, ld_s, TR_N, d.dim, dim4, d.kp, d.pool_dt, kvvec, VY_UACT_NONE,
+                         [&](int j) { return krow_s[j] >= 0 ? (static_cast<long long>(krow_s[j]) * G + g) * d.dim : -1LL; });
+      __syncthreads();
+      for (int it = t; it < per * TR_N; it += TR_T) {
+        const int hh = it / TR_N, j = it - hh * TR_N, h = g * per + hh;
+        const float* qp = q_s + h * dim4;
+        const float* kp = kv_s + j * ld_s;
+        float a = 0.f;
+        for (int c = 0; c < dim4; c += 4) a = dot4(f4(qp + c), f4(kp + c), a);
+        S_s[h * TR_N + j] = cap_score(a * d.scale, d.softcap);
+      }
+    }
+    __syncthreads();
+    for (int it = t; it < H * TR_N; it += TR_T) {
+      const int h = it / TR_N, j = it - h * TR_N;
+      float a = 0.f;
+      for (int b = 0; b < H; ++b) a = fmaf(T_s[h * H + b], S_s[b * TR_N + j], a);
+      P_s[it] = j < nk ? a : -INFINITY;
+    }
+    __syncthreads();
+    for (int h = warp; h < H; h += TR_T / 32) {
+      float* pr = P_s + h * TR_N;
+      const float a = pr[lane], b = pr[lane + 32];
+      const float mo = m_s[h];
+      const float mn = fmaxf(mo, warp_max(fmaxf(a, b)));
+      const float cr = mn == -INFINITY ? 1.f : expf(mo - mn);
+      const float pa = a == -INFINITY ? 0.f : expf(a - mn), pb = b == -INFINITY ? 0.f : expf(b - mn);
+      pr[lane] = pa;
+      pr[lane + 32] = pb;
+      const float sum = warp_sum(pa + pb);
+      if (lane == 0) {
+        l_s[h] = fmaf(l_s[h], cr, sum);
+        m_s[h] = mn;
+        c_s[h] = cr;
+      }
+    }
+    for (int g = 0; g < G; ++g) {
+      __syncthreads();
+      rows_to_smem<TR_T>(kv_s, ld_s, TR_N, d.vdim, vdim4, d.vp, d.pool_dt, kvvec, VY_UACT_NONE,
+                         [&](int j) { return krow_s[j] >= 0 ? (static_cast<long long>(krow_s[j]) * G + g) * d.vdim : -1LL; });
+      __syncthreads();
+      for (int o = t; o < per * d.vdim; o += TR_T) {
+        const int hh = o / d.vdim, c = o - hh * d.vdim, h = g * per + hh;
+        const float* pr = P_s + h * TR_N;
+        float a = acc_s[h * d.vdim + c] * c_s[h];
+        for (int j = 0; j < nk; ++j) a = fmaf(pr[j], kv_s[j * ld_s + c], a);
+        acc_s[h * d.vdim + c] = a;
+      }
+    }
+  }
+  __syncthreads();
+  if (splits == 1) {
+    for (int o = t; o < H * d.vdim; o += TR_T) {
+      const int h = o / d.vdim, c = o - h * d.vdim;
+      const float l = l_s[h];
+      st_from_float(d.out, d.out_dt, qrow * d.ld_out + o, l > 0.f ? acc_s[o] / l * gate_of(d, qrow, h, c) : 0.f);
+    }
+  } else {
+    // part of (row, split): [H] max | [H] sum | [H * vdim] unnormalised output
+    float* w = ws + (qrow * splits + split) * static_cast<long long>(H) * (d.vdim + 2);
+    for (int h = t; h < H; h += TR_T) {
+      w[h] = m_s[h];
+      w[H + h] = l_s[h];
+    }
+    for (int o = t; o < H * d.vdim; o += TR_T) w[2 * H + o] = acc_s[o];
+  }
+}
+
+// one CTA per row: combines the splits' parts, adds the sink term, gates and stores
+__global__ void __launch_bounds__(128) talk_attn_merge_kernel(TalkDev d, int rows, int splits, const float* ws) {
+  pdl_trigger();
+  pdl_wait();
+  const long long row = blockIdx.x;
+  const int H = d.heads;
+  const float* w0 = ws + row * splits * static_cast<long long>(H) * (d.vdim + 2);
+  const long long part = static_cast<long long>(H) * (d.vdim + 2);
+  for (int o = threadIdx.x; o < H * d.vdim; o += blockDim.x) {
+    const int h = o / d.vdim, c = o - h * d.vdim;
+    float sk;
+    const bool has = sink_of(d, h, sk);
+    float m = has ? sk : -INFINITY;
+    for (int k = 0; k < splits; ++k) m = fmaxf(m, w0[k * part + h]);
+    float l = has ? expf(sk - m) : 0.f, a = 0.f;
+    for (int k = 0; k < splits; ++k) {
+      const float mk = w0[k * part + h];
+      if (mk == -INFINITY) continue;
+      const float f = expf(mk - m);
+      l = fmaf(w0[k * part + H + h], f, l);
+      a = fmaf(w0[k * part + 2 * H + o], f, a);
+    }
+    st_from_float(d.out, d.out_dt, row * d.ld_out + o, l > 0.f ? a / l * gate_of(d, row, h, c) : 0.f);
+  }
+}
+
+// ---- tiled form -------------------------------------------------------------------------------------------------------------------
+// Rows r = h * TQ + i (head h, query i of the tile); RB blocks of 64 rows. Thread (ti, tj) of the 16 x 16 grid owns rows
+// 64 b + 4 ti .. + 3 (the same head: TQ is a multiple of 4) and key columns tj (+ 16) in the score phase, and the value
+// columns 4 (tj + 16 mm) .. + 3 of those rows in the output phase. Per key tile: the key rows of every key/value head go to
+// shared memory ([kv head][key][channel]), each thread contracts its rows with its head's keys, the exchange reads every head's raw
+// scores, the online softmax runs by warps over rows, then the value rows replace the keys and are accumulated.
+constexpr int TT_T = 256;
+
+template <int RB, int MV, int KN>   // KN keys per tile: 32, or 16 when many wide key/value heads would not fit otherwise
+__global__ void __launch_bounds__(TT_T, RB == 1 ? 2 : 1)
+talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ldkv, bool qvec, bool kvvec) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int R = 64 * RB, LDP = KN + 4, NCB = KN / 16;
+  extern __shared__ __align__(16) float tt_smem[];
+  const int H = d.heads, G = d.kv_heads, per = H / G;
+  float* Q_s = tt_smem;                    // [R][ldq_s]
+  float* K_s = Q_s + R * ldq_s;            // [G][KN][ldkv]  (keys, then values)
+  float* S_s = K_s + G * KN * ldkv;        // [R][LDP] raw scores
+  float* P_s = S_s + R * LDP;              // [R][LDP] mixed scores, then weights
+  float* T_s = P_s + R * LDP;              // [H][H]
+  float* corr_s = T_s + H * H;             // [R]
+  float* l_out = corr_s + R;               // [R]
+  int* krow_s = reinterpret_cast<int*>(l_out + R);   // [KN]
+  const int s = blockIdx.y, i0 = blockIdx.x * TQ;
+  const int t = threadIdx.x, ti = t >> 4, tj = t & 15, warp = t >> 5, lane = t & 31;
+  const int base = d.cu[s], n = d.cu[s + 1] - base;
+  if (i0 >= n) return;
+  const int nq = min(TQ, n - i0);
+  const int rows = H * TQ;   // <= R
+  rows_to_smem<TT_T>(Q_s, ldq_s, R, d.dim, dim4, d.q, d.q_dt, qvec, VY_UACT_NONE, [&](int r) {
+    const int h = r / TQ, i = r - h * TQ;
+    return (r < rows && i < nq) ? static_cast<long long>(base + i0 + i) * d.ldq + static_cast<long long>(h) * d.dim : -1LL;
+  });
+  for (int e = t; e < H * H; e += TT_T) T_s[e] = d.talk ? ld_as_float(d.talk, d.talk_dt, e) : (e / H == e % H ? 1.f : 0.f);
+  const int p_lo = d.pos0[s] + i0, p_hi = p_lo + nq - 1;
+  const int lo = d.window > 0 ? max(p_lo - d.window + 1, 0) : 0;
+  const int count = p_hi - lo + 1;
+  const int* tab = d.table + static_cast<long long>(s) * d.tw;
+  constexpr int RPW = R / 8;   // rows per warp in the softmax phase
+  float m[RPW], l[RPW];
+#pragma unroll
+  for (int rr = 0; rr < RPW; ++rr) {
+    const int r = warp * RPW + rr;
+    float sk;
+    const bool has = r < rows && sink_of(d, r / TQ, sk);
+    m[rr] = has ? sk : -INFINITY;
+    l[rr] = has ? 1.f : 0.f;
+  }
+  float acc[RB][4][MV][4];
+  int kvoff[RB];   // this thread's rows read the staged rows of their key/value head: K_s + kvoff
+#pragma unroll
+  for (int b = 0; b < RB; ++b) {
+    const int r0 = 64 * b + 4 * ti;
+    kvoff[b] = r0 < rows ? (r0 / TQ / per) * KN * ldkv : -1;
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int mm = 0; mm < MV; ++mm)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[b][r][mm][e] = 0.f;
+  }
+
+  for (int c0 = 0; c0 < count; c0 += KN) {
+    const int nk = min(KN, count - c0);
+    __syncthreads();
+    if (t < KN) {
+      const int kp = lo + c0 + t;
+      krow_s[t] = t < nk ? tab[kp / d.bs] * d.bs + kp % d.bs : -1;
+    }
+    __syncthreads();
+    rows_to_smem<TT_T>(K_s, ldkv, G * KN, d.dim, dim4, d.kp, d.pool_dt, kvvec, VY_UACT_NONE, [&](int jj) {
+      const int g = jj / KN, j = jj - g * KN;
+      return krow_s[j] >= 0 ? (static_cast<long long>(krow_s[j]) * G + g) * d.dim : -1LL;
+    });
+    __syncthreads();
+    // raw scores
+#pragma unroll
+    for (int b = 0; b < RB; ++b) {
+      if (kvoff[b] < 0) continue;
+      const int r0 = 64 * b + 4 * ti;
+      const float* Kg = K_s + kvoff[b];
+      float sc[4][NCB];
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < NCB; ++c) sc[r][c] = 0.f;
+#pragma unroll 2
+      for (int c = 0; c < dim4; c += 4) {
+        float4 kv[NCB];
+#pragma unroll
+        for (int cb = 0; cb < NCB; ++cb) kv[cb] = f4(Kg + (tj + 16 * cb) * ldkv + c);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float4 qv = f4(Q_s + (r0 + r) * ldq_s + c);
+#pragma unroll
+          for (int cb = 0; cb < NCB; ++cb) sc[r][cb] = dot4(qv, kv[cb], sc[r][cb]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int cb = 0; cb < NCB; ++cb) S_s[(r0 + r) * LDP + tj + 16 * cb] = cap_score(sc[r][cb] * d.scale, d.softcap);
+    }
+    __syncthreads();
+    // values replace the keys while the exchange and the softmax run from S_s / P_s
+    rows_to_smem<TT_T>(K_s, ldkv, G * KN, d.vdim, vdim4, d.vp, d.pool_dt, kvvec, VY_UACT_NONE, [&](int jj) {
+      const int g = jj / KN, j = jj - g * KN;
+      return krow_s[j] >= 0 ? (static_cast<long long>(krow_s[j]) * G + g) * d.vdim : -1LL;
+    });
+    // exchange + mask: element (h, i, j) of P = sum_b talk[h, b] S[b, i, j]
+    for (int it = t; it < rows * (KN / 4); it += TT_T) {
+      const int r = it / (KN / 4), j4 = (it - r * (KN / 4)) * 4;
+      const int h = r / TQ, i = r - h * TQ;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int b = 0; b < H; ++b) {
+        const float w = T_s[h * H + b];
+        const float4 x = f4(S_s + (b * TQ + i) * LDP + j4);
+        a.x = fmaf(w, x.x, a.x); a.y = fmaf(w, x.y, a.y); a.z = fmaf(w, x.z, a.z); a.w = fmaf(w, x.w, a.w);
+      }
+      const int pq = p_lo + i, kp0 = lo + c0 + j4;
+      const bool live = i < nq;
+      float* pr = P_s + r * LDP + j4;
+      const auto vis = [&](int kp, int j) { return live && j < nk && kp <= pq && (d.window <= 0 || pq - kp < d.window); };
+      pr[0] = vis(kp0, j4) ? a.x : -INFINITY;
+      pr[1] = vis(kp0 + 1, j4 + 1) ? a.y : -INFINITY;
+      pr[2] = vis(kp0 + 2, j4 + 2) ? a.z : -INFINITY;
+      pr[3] = vis(kp0 + 3, j4 + 3) ? a.w : -INFINITY;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int rr = 0; rr < RPW; ++rr) {
+      const int r = warp * RPW + rr;
+      float* pr = P_s + r * LDP;
+      const float a = (r < rows && lane < KN) ? pr[lane] : -INFINITY;
+      const float mn = fmaxf(m[rr], warp_max(a));
+      const float cr = mn == -INFINITY ? 1.f : expf(m[rr] - mn);
+      const float pa = a == -INFINITY ? 0.f : expf(a - mn);
+      if (lane < KN) pr[lane] = pa;
+      l[rr] = fmaf(l[rr], cr, warp_sum(pa));
+      m[rr] = mn;
+      if (lane == 0) corr_s[r] = cr;
+    }
+    __syncthreads();
+    // values
+    const int nv = (nk + 3) & ~3;
+#pragma unroll
+    for (int b = 0; b < RB; ++b) {
+      if (kvoff[b] < 0) continue;
+      const int r0 = 64 * b + 4 * ti;
+      const float* Vg = K_s + kvoff[b];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float cr = corr_s[r0 + r];
+#pragma unroll
+        for (int mm = 0; mm < MV; ++mm)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[b][r][mm][e] *= cr;
+      }
+      for (int j4 = 0; j4 < nv; j4 += 4) {
+        float4 pv[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) pv[r] = f4(P_s + (r0 + r) * LDP + j4);
+#pragma unroll
+        for (int mm = 0; mm < MV; ++mm) {
+          const int col = 4 * (tj + 16 * mm);
+          if (col < vdim4) {
+            const float4 x0 = f4(Vg + (j4 + 0) * ldkv + col), x1 = f4(Vg + (j4 + 1) * ldkv + col);
+            const float4 x2 = f4(Vg + (j4 + 2) * ldkv + col), x3 = f4(Vg + (j4 + 3) * ldkv + col);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              axpy4(acc[b][r][mm], pv[r].x, x0);
+              axpy4(acc[b][r][mm], pv[r].y, x1);
+              axpy4(acc[b][r][mm], pv[r].z, x2);
+              axpy4(acc[b][r][mm], pv[r].w, x3);
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int rr = 0; rr < RPW; ++rr) l_out[warp * RPW + rr] = l[rr];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int b = 0; b < RB; ++b)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int row = 64 * b + 4 * ti + r;
+      if (row >= rows) continue;
+      const int h = row / TQ, i = row - h * TQ;
+      if (i >= nq) continue;
+      const long long qrow = base + i0 + i;
+      const float lv = l_out[row];
+      const float inv = lv > 0.f ? 1.f / lv : 0.f;
+#pragma unroll
+      for (int mm = 0; mm < MV; ++mm)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = 4 * (tj + 16 * mm) + e;
+          if (col < d.vdim)
+            st_from_float(d.out, d.out_dt, qrow * d.ld_out + static_cast<long long>(h) * d.vdim + col, acc[b][r][mm][e] * inv * gate_of(d, qrow, h, col));
+        }
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------------------------------
+static int rows_splits(int n_seqs, int max_new, int table_width, int block_size) {
+  // single-token steps only: enough CTAs for two waves of the SMs, at most one per key tile, at most 64
+  if (max_new != 1) return 1;
+  const long long rows = static_cast<long long>(n_seqs) * max_new;
+  const long long max_tiles = (static_cast<long long>(table_width) * block_size + TR_N - 1) / TR_N;
+  long long want = (2 * 148 + rows - 1) / rows;
+  if (want > max_tiles) want = max_tiles;
+  if (want > 64) want = 64;
+  return want < 1 ? 1 : static_cast<int>(want);
+}
+
+static size_t rows_smem(const TalkDev& d, int dim4, int ld_s) {
+  const size_t H = d.heads;
+  return sizeof(float) * (H * dim4 + static_cast<size_t>(TR_N) * ld_s + 2 * H * TR_N + H * H + 3 * H + H * d.vdim) + sizeof(int) * TR_N;
+}
+
+static int pad_ld(int w4) { return ((w4 >> 2) & 1) ? w4 + 8 : w4 + 4; }   // (row stride / 4) odd: rows 1 apart start in distinct 16-byte bank groups
+
+struct TiledPlan { int RB, MV, KN, TQ, ldq_s, ldkv; size_t smem; bool ok; };
+
+static TiledPlan tiled_plan(const TalkDev& d, int dim4, int vdim4) {
+  TiledPlan pl;
+  memset(&pl, 0, sizeof(pl));
+  const int H = d.heads;
+  if (H * 4 > 128 || d.vdim > 128) return pl;
+  pl.MV = d.vdim <= 64 ? 1 : 2;
+  pl.RB = H * 4 <= 64 ? 1 : 2;
+  const int R = 64 * pl.RB;
+  pl.TQ = (R / H) & ~3;   // queries per tile: a multiple of 4, so the 4 rows of a thread share a head
+  pl.ldq_s = pad_ld(dim4);
+  pl.ldkv = pad_ld(dim4 > vdim4 ? dim4 : vdim4);
+  for (pl.KN = 32; pl.KN >= 16; pl.KN >>= 1) {
+    pl.smem = sizeof(float) * (static_cast<size_t>(R) * pl.ldq_s + static_cast<size_t>(d.kv_heads) * pl.KN * pl.ldkv + 2 * static_cast<size_t>(R) * (pl.KN + 4) +
+                               static_cast<size_t>(H) * H + 2 * R) + sizeof(int) * pl.KN;
+    // 32-key tiles when two CTAs fit an SM with them or nothing smaller is needed; 16-key tiles when 32 do not fit at all
+    if (pl.smem <= 200 * 1024) { pl.ok = true; break; }
+  }
+  return pl;
+}
+
+template <int RB, int MV, int KN>
+static cudaError_t launch_tiled_kn(const TalkDev& d, const TiledPlan& pl, int n_seqs, int max_new, int dim4, int vdim4, bool qvec, bool kvvec, cudaStream_t st) {
+  static size_t allowed = 48 * 1024;
+  if (pl.smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(talk_attn_tiled_kernel<RB, MV, KN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem));
+    if (e != cudaSuccess) return e;
+    allowed = pl.smem;
+  }
+  return launch_kernel(talk_attn_tiled_kernel<RB, MV, KN>, dim3((max_new + pl.TQ - 1) / pl.TQ, n_seqs), dim3(TT_T), pl.smem, st, d, pl.TQ, dim4, vdim4,
+                       pl.ldq_s, pl.ldkv, qvec, kvvec);
+}
+template <int RB, int MV>
+static cudaError_t launch_tiled(const TalkDev& d, const TiledPlan& pl, int n_seqs, int max_new, int dim4, int vdim4, bool qvec, bool kvvec, cudaStream_t st) {
+  return pl.KN == 32 ? launch_tiled_kn<RB, MV, 32>(d, pl, n_seqs, max_new, dim4, vdim4, qvec, kvvec, st)
+                     : launch_tiled_kn<RB, MV, 16>(d, pl, n_seqs, max_new, dim4, vdim4, qvec, kvvec, st);
+}
+
+}  // namespace vy
+
+#define VY_NEED_DEVICE(name)                                                   \
+  if (!vy_device_ok()) {                                                       \
+    ::vy::set_error(name ": no sm_100 device (there is no CPU fallback)");     \
+    return VY_ERR_NO_DEVICE;                                                   \
+  }
+
+extern "C" int64_t vy_talk_attn_workspace_floats(int32_t n_seqs, int32_t max_new, int32_t table_width, int32_t block_size, int32_t heads, int32_t vdim) {
+  if (n_seqs <= 0 || max_new <= 0) return 0;
+  const int splits = vy::rows_splits(n_seqs, max_new, table_width, block_size);
+  if (splits <= 1) return 0;
+  return static_cast<int64_t>(n_seqs) * max_new * splits * heads * (vdim + 2);
+}
+
+extern "C" int vy_talk_attn(const VyTalkAttn* p) {
+  using namespace vy;
+  VY_CHECK_ARG(p != nullptr, "vy_talk_attn: null params");
+  VY_NEED_DEVICE("vy_talk_attn");
+  VY_CHECK_ARG(p->n_seqs > 0 && p->n_seqs <= 65535 && p->max_new > 0 && p->cu_tokens && p->pos0 && p->block_table && p->block_size > 0 &&
+                   p->table_width > 0, "vy_talk_attn: bad batch");
+  VY_CHECK_ARG(p->heads > 0 && p->heads <= 1024 && p->kv_heads > 0 && p->heads % p->kv_heads == 0 && p->dim > 0 && p->vdim > 0,
+               "vy_talk_attn: heads %d must be a multiple of kv_heads %d; dim %d, vdim %d", p->heads, p->kv_heads, p->dim, p->vdim);
+  VY_CHECK_ARG(p->q && p->k_pool && p->v_pool && p->out && dtype_ok(p->q_dtype) && dtype_ok(p->pool_dtype) && dtype_ok(p->out_dtype) &&
+                   (!p->talk || dtype_ok(p->talk_dtype)) && (!p->sink || dtype_ok(p->sink_dtype)) && (!p->gate || dtype_ok(p->gate_dtype)),
+               "vy_talk_attn: bad tensors");
+  TalkDev d;
+  d.cu = p->cu_tokens; d.pos0 = p->pos0; d.table = p->block_table; d.tw = p->table_width; d.bs = p->block_size;
+  d.q = p->q; d.ldq = p->ldq; d.q_dt = p->q_dtype;
+  d.kp = p->k_pool; d.vp = p->v_pool; d.pool_dt = p->pool_dtype;
+  d.heads = p->heads; d.kv_heads = p->kv_heads; d.dim = p->dim; d.vdim = p->vdim;
+  d.scale = p->scale; d.softcap = p->softcap; d.window = p->window;
+  d.talk = p->talk; d.talk_dt = p->talk_dtype;
+  d.sink = p->sink; d.sink_dt = p->sink_dtype; d.zero_sink = p->zero_sink;
+  d.gate = p->gate; d.ld_gate = p->ld_gate; d.gate_dt = p->gate_dtype; d.gate_ch = p->gate_per_channel;
+  d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
+  cudaStream_t st = static_cast<cudaStream_t>(p->stream);
+  const int dim4 = (d.dim + 3) & ~3, vdim4 = (d.vdim + 3) & ~3;
+  const auto al = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+  const bool qvec = d.q_dt == VY_F32 && d.dim % 4 == 0 && d.ldq % 4 == 0 && al(d.q);
+  const bool kvvec = d.pool_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && al(d.kp) && al(d.vp);
+  const TiledPlan pl = tiled_plan(d, dim4, vdim4);
+  VY_CHECK_ARG(p->force_form != 2 || pl.ok, "vy_talk_attn: the tiled form takes heads <= 32 and vdim <= 128 within 200 KB of shared memory");
+  const bool tiled = p->force_form == 2 || (p->force_form == 0 && pl.ok && p->max_new >= 8);
+  if (tiled) {
+    cudaError_t e;
+    if (pl.RB == 1) e = pl.MV == 1 ? launch_tiled<1, 1>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st)
+                                   : launch_tiled<1, 2>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st);
+    else e = pl.MV == 1 ? launch_tiled<2, 1>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st)
+                        : launch_tiled<2, 2>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st);
+    VY_CUDA_OK(e);
+    VY_LAUNCH_OK();
+    count_launch();
+    return VY_OK;
+  }
+  const int ld_s = pad_ld(dim4 > vdim4 ? dim4 : vdim4);
+  const size_t smem = rows_smem(d, dim4, ld_s);
+  VY_CHECK_ARG(smem <= 220 * 1024, "vy_talk_attn: %d heads of %d / %d channels need %zu bytes of shared memory per CTA (at most 220 KB)", d.heads, d.dim,
+               d.vdim, smem);
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    VY_CUDA_OK(cudaFuncSetAttribute(talk_attn_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    allowed = smem;
+  }
+  int splits = rows_splits(p->n_seqs, p->max_new, p->table_width, p->block_size);
+  const long long rows_bound = static_cast<long long>(p->n_seqs) * p->max_new;
+  if (splits > 1) {
+    const long long need = rows_bound * splits * d.heads * (d.vdim + 2);
+    if (!p->workspace || p->workspace_floats < need) splits = 1;   // no scratch given: every query walks all its keys in one CTA
+  }
+  VY_CUDA_OK(launch_kernel(talk_attn_rows_kernel, dim3(p->max_new, p->n_seqs, splits), dim3(TR_T), smem, st, d, dim4, vdim4, ld_s, qvec, kvvec, splits,
+                           p->workspace));
+  VY_LAUNCH_OK();
+  count_launch();
+  if (splits > 1) {   // single-token steps: row s is sequence s
+    VY_CUDA_OK(launch_kernel(talk_attn_merge_kernel, dim3(static_cast<unsigned>(p->n_seqs)), dim3(128), 0, st, d, p->n_seqs, splits,
+                             static_cast<const float*>(p->workspace)));
+    VY_LAUNCH_OK();
+    count_launch();
+  }
+  return VY_OK;
+}

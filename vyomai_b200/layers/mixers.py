@@ -1,5 +1,5 @@
-"""Sequence mixers and feed-forwards of the packed-step decoder families (models/gelutar.py, models/zugunex.py), on the
-packed-batch kernels of csrc/seqmix.cu and csrc/latent.cu. Each mixer is built from its config block and its weights, declares what it keeps per sequence
+"""Sequence mixers and feed-forwards of the packed-step decoder families (models/gelutar.py, models/zugunex.py, models/vazepel.py),
+on the packed-batch kernels of csrc/seqmix.cu, csrc/latent.cu, csrc/talking_attn.cu and csrc/parallel_block.cu. Each mixer is built from its config block and its weights, declares what it keeps per sequence
 (`cache_spec`: pages of keys / values, recurrent state slots) and maps the normed layer input h [rows, width] to its
 output; the constants of a mechanism (window, kept tokens, scale, sink, decay, taps, head counts) are constructor
 arguments, so another architecture can reuse a mixer with other values.
@@ -38,10 +38,10 @@ class Projection:
         N = self.out_features
         if out is None:
             out = torch.empty((x.shape[0], _round_up(N, 8)), device=x.device, dtype=out_dtype)[:, :N]
-        tc = self.tensor_cores and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and bias is None \
+        tc = self.tensor_cores and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 \
             and act in (None, "none", "relu2", "gelu_tanh")
         if tc:
-            ops.gemm(x, self.weight, act=act, addend=addend, out=out, out_scale=scale, swap_ab=x.shape[0] <= 32)
+            ops.gemm(x, self.weight, bias=bias, act=act, addend=addend, out=out, out_scale=scale, swap_ab=x.shape[0] <= 32)
         else:
             ops.linear_plain(x, self.weight, bias=bias, act=act, scale=scale, addend=addend, out=out)
         return out
@@ -62,13 +62,27 @@ def pack_rows(tensors: List[torch.Tensor], align: int = 8) -> Tuple[torch.Tensor
     return w, spans
 
 
+def pack_biases(spans: List[Tuple[int, int]], total: int, biases: List[Optional[torch.Tensor]], like: torch.Tensor) -> Optional[torch.Tensor]:
+    """The bias of a packed projection: each block's bias at the block's offset, zero where a block has none (None when no block has one)."""
+    if not any(b is not None for b in biases):
+        return None
+    out = torch.zeros(total, dtype=like.dtype, device=like.device)
+    for (o, n), b in zip(spans, biases):
+        if b is not None:
+            out[o:o + n] = b
+    return out
+
+
 class Mixer:
     """Common surface: `cache_spec()` -> {"pages": (kv_heads, dim, vdim) | None, "states": {name: per-slot shape}};
-    `input_weights()` -> the [out, in] matrices that read the layer input (packed by the layer into one projection);
-    `forward(parts, batch, cache)` with `parts` the list of product blocks in the same order."""
+    `input_weights()` -> the [out, in] matrices that read the layer input (packed by the layer into one projection), `input_biases()` ->
+    their biases (None entries for none); `forward(parts, batch, cache)` with `parts` the list of product blocks in the same order."""
 
     def cache_spec(self) -> dict:
         return {"pages": None, "states": {}}
+
+    def input_biases(self):
+        return [None] * len(self.input_weights())
 
 
 class LightningMixer(Mixer):
@@ -294,6 +308,57 @@ class LatentAttention(Mixer):
         return self.o(o)
 
 
+class TalkingHeadsAttention(Mixer):
+    """Grouped-query softmax attention whose heads exchange scores: biased q / k / v projections, pair rotation by position on the
+    leading rot.dims entries of every head, score = cap tanh(q.k scale / cap), the scores of all heads mixed through a [heads, heads]
+    matrix before the softmax, causal (optionally windowed) mask, a sink in the denominator (`sink`: "zero" = a term of score 0,
+    "learned" = the per-head tensor `sink`, None = none), a per-channel sigmoid output gate read from the layer input and a biased
+    output projection. Keys (rotated) and values live in pages."""
+
+    def __init__(self, cfg: dict, w: Dict[str, torch.Tensor], eps: float, act_dtype: torch.dtype, tensor_cores: bool,
+                 kv_dtype: torch.dtype = torch.float32, sink: Optional[str] = "zero"):
+        self.heads, self.kv_heads = int(cfg["heads"]), int(cfg["kv_heads"])
+        self.dim, self.vdim = int(cfg["dim"]), int(cfg["vdim"])
+        if self.heads % self.kv_heads:
+            raise ValueError("attention: heads must be a multiple of kv_heads")
+        rot = cfg.get("rot") or {}
+        self.rot_dims = int(rot.get("dims", 0))
+        if self.rot_dims > self.dim or self.rot_dims % 2:
+            raise ValueError("attention: rot.dims must be even and at most dim")
+        base = float(rot.get("base", 10000.0))
+        f = [base ** (-2.0 * i / self.rot_dims) for i in range(self.rot_dims // 2)] or [0.0]
+        dev = w["q"].device
+        self.inv_freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(dev)
+        self.scale, self.softcap = float(cfg["scale"]), float(cfg.get("softcap") or 0.0)
+        self.window = int((cfg.get("mask") or {}).get("size", 0))
+        self.eps, self.act_dtype, self.kv_dtype = eps, act_dtype, kv_dtype
+        self._in = [w["q"], w["k"], w["v"], w["g"]]
+        self._in_b = [w.get("q.b"), w.get("k.b"), w.get("v.b"), w.get("g.b")]
+        self.talk = w["talk"].to(torch.float32).contiguous() if "talk" in w else None
+        self.sink_kind = sink
+        self.sink = w["sink"].contiguous() if sink == "learned" else None
+        self.o = Projection(w["o"], tensor_cores)
+        self.o_bias = w["o.b"].contiguous() if "o.b" in w else None
+
+    def input_weights(self):
+        return self._in
+
+    def input_biases(self):
+        return self._in_b
+
+    def cache_spec(self):
+        return {"pages": (self.kv_heads, self.dim, self.vdim), "states": {}, "kv_dtype": self.kv_dtype}
+
+    def forward(self, parts, batch, cache, form: Optional[str] = None):
+        q, k, v, g = parts
+        ops.rope_kv_write(batch, q, k, v, self.inv_freq, cache.k_pool, cache.v_pool, heads=self.heads, kv_heads=self.kv_heads, dim=self.dim,
+                          vdim=self.vdim, rot_dims=self.rot_dims)
+        a = ops.talk_attn(batch, q, cache.k_pool, cache.v_pool, heads=self.heads, kv_heads=self.kv_heads, dim=self.dim, vdim=self.vdim,
+                          scale=self.scale, softcap=self.softcap, talk=self.talk, window=self.window, sink=self.sink,
+                          zero_sink=self.sink_kind == "zero", gate=g, gate_per_channel=True, out_dtype=self.act_dtype, form=form)
+        return self.o(a, bias=self.o_bias)
+
+
 class DenseMLP:
     """W_down act(W_up h). With `x_residual` the down projection adds into the fp32 residual in its epilogue; without, it
     returns the fp32 result (models that norm a sublayer's OUTPUT)."""
@@ -317,10 +382,16 @@ class ReluSquaredMLP(DenseMLP):
 
 
 class MoEFeedForward:
-    """Mixture of experts W_down_e act(W_up_e h) with a sigmoid router: the `top` largest scores are kept, divided by their sum
-    and multiplied by `route_scale`; an optional shared expert runs for every token, times sigmoid(w_sg . h). Router logits and
-    the shared gate are one product with fp32 accumulation and an fp32 result (its input is the layer input as the experts read
-    it: bf16-rounded when the model's projections are); scores, selection and weights are fp32.
+    """Mixture of experts with an optional shared expert that runs for every token. Router logits (and the shared gate) are one
+    product with fp32 accumulation and an fp32 result (its input is the layer input as the experts read it: bf16-rounded when the
+    model's projections are); scores, selection and weights are fp32.
+
+    Router (`router`): "sigmoid" scores or the "softmax" over all experts; with `groups` = (count, keep) only members of the `keep`
+    best of `count` runs of neighbouring experts are eligible; the `top` largest eligible scores are kept and, with `normalize`,
+    divided by their sum; times `route_scale`.
+    Expert (`form`): "plain" = W_down act(W_up h); "glu" = W_down (g sigmoid(alpha g) (u + 1)) with g = min(W_gate h, limit),
+    u = clamp(W_up h, +-limit) (the shared expert with `shared_limit`). The shared expert is weighted by sigmoid(w_sg . h) when the
+    weights hold `shared.sg`, by 1 otherwise.
 
     Two exact forms of the same sum. Single tokens and short steps (also every CUDA-graph-captured step: no host decision)
     run ALL experts as two products over the concatenated experts, the hidden activations multiplied by each token's routing
@@ -335,53 +406,78 @@ class MoEFeedForward:
     LAUNCH_COST = 15e-6                   # host time of one product issued from Python (s): what bounds many small launches
 
     def __init__(self, w: Dict[str, torch.Tensor], experts: int, top: int, route_scale: float, act_dtype: torch.dtype, tensor_cores: bool,
-                 act: str = "relu2", shared: bool = False, sorted_min_rows: int = 128, force_sorted: bool = False):
+                 act: str = "relu2", shared: bool = False, sorted_min_rows: int = 128, force_sorted: bool = False, router: str = "sigmoid",
+                 groups: Optional[Tuple[int, int]] = None, normalize: bool = True, form: str = "plain", limit: float = 0.0,
+                 shared_limit: float = 0.0, alpha: float = 1.702, router_logits: bool = True):
         self.experts, self.top, self.route_scale = int(experts), int(top), float(route_scale)
         self.act_dtype, self.act, self.sorted_min_rows, self.force_sorted = act_dtype, act, int(sorted_min_rows), bool(force_sorted)
+        self.router_kind, self.normalize = router, bool(normalize)
+        self.groups, self.keep_groups = (int(groups[0]), int(groups[1])) if groups and int(groups[0]) > 1 else (0, 0)
+        if self.groups and (self.experts % self.groups or not 0 < self.keep_groups <= self.groups or self.top > self.keep_groups * (self.experts // self.groups)):
+            raise ValueError("experts: the groups must divide the experts, and the kept groups hold at least `top` experts")
+        if form not in ("plain", "glu"):
+            raise ValueError(f"experts: unknown form {form!r}")
+        self.glu, self.limit, self.shared_limit, self.alpha = form == "glu", float(limit), float(shared_limit), float(alpha)
         E = self.experts
         self.ff = w["e0.up"].shape[0]
-        ups = [w[f"e{e}.up"] for e in range(E)]
+        hid = (lambda pre: torch.cat([w[pre + "gate"], w[pre + "up"]], 0)) if self.glu else (lambda pre: w[pre + "up"])
+        ups = [hid(f"e{e}.") for e in range(E)]
         downs = [w[f"e{e}.down"] for e in range(E)]
         self.shared_ff = 0
+        self.shared_gated = shared and "shared.sg" in w
         rt = [w["router"]]
         if shared:
             self.shared_ff = w["shared.up"].shape[0]
-            ups.append(w["shared.up"])
+            ups.append(hid("shared."))
             downs.append(w["shared.down"])
-            rt.append(w["shared.sg"].reshape(1, -1))
-        up_all = torch.cat(ups, 0).contiguous()        # [E ff + S, W]
+            if self.shared_gated:
+                rt.append(w["shared.sg"].reshape(1, -1))
+        up_all = torch.cat(ups, 0).contiguous()        # [E ff + S, W]  (glu: [E 2 ff + 2 S, W], per expert [gate | up])
         down_all = torch.cat(downs, 1).contiguous()    # [W, E ff + S]
         self.up_all, self.down_all = Projection(up_all, tensor_cores), Projection(down_all, tensor_cores)
-        self.router = Projection(torch.cat(rt, 0).contiguous(), tensor_cores)    # [E (+ 1), W]
-        f = self.ff
-        self.up_e = [Projection(up_all[e * f:(e + 1) * f], tensor_cores) for e in range(E)]
+        # the router's rows (+ the shared gate's); a layer that packs them into its input projection hands the logits to forward()
+        self.router_weight = torch.cat(rt, 0).contiguous()    # [E (+ 1), W]
+        self.router = Projection(self.router_weight, tensor_cores) if router_logits else None
+        f, fu = self.ff, self.ff * (2 if self.glu else 1)
+        self.up_e = [Projection(up_all[e * fu:(e + 1) * fu], tensor_cores) for e in range(E)]
         self.down_e = [Projection(down_all[:, e * f:(e + 1) * f], tensor_cores) for e in range(E)]
         if shared:
-            self.up_s = Projection(up_all[E * f:], tensor_cores)
+            self.up_s = Projection(up_all[E * fu:], tensor_cores)
             self.down_s = Projection(down_all[:, E * f:], tensor_cores)
 
     def _sorted_is_faster(self, rows: int) -> bool:
         width = self.down_all.out_features
         rate = self.TC_RATE if self.up_all.tensor_cores and self.act_dtype == torch.bfloat16 else self.FMA_RATE
-        per_choice = 4.0 * rows * self.ff * width / rate   # up + down multiply-adds of one expert-sized slice over all rows
+        per_choice = (6.0 if self.glu else 4.0) * rows * self.ff * width / rate   # up (+ gate) + down multiply-adds of one expert-sized slice over all rows
         moved = 3.0 * rows * self.top * width * 4 / 2.0e12   # gather, per-pair results, combine
         return self.top * per_choice + 2 * self.experts * self.LAUNCH_COST + moved < self.experts * per_choice
 
-    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
-        """h: the layer input in the activation dtype. Returns fp32 [rows, width]."""
+    def _hidden(self, proj: Projection, x: torch.Tensor, dense: Optional[torch.Tensor], experts: int, shared_ff: int, sg, wide: bool) -> torch.Tensor:
+        """The activated (and, with `dense`, weighted) hidden rows of `experts` experts and / or the shared expert, in the activation dtype."""
+        if self.glu:
+            u = proj(x)   # fp32 pre-activations: the clamps and the gate see the accumulator, rounded once after the activation
+            return ops.moe_glu(u, dense, experts=experts, ff=self.ff, shared_ff=shared_ff, limit=self.limit, shared_limit=self.shared_limit,
+                               alpha=self.alpha, out_dtype=self.act_dtype)
+        u = proj(x, act=self.act, out_dtype=self.act_dtype if wide else torch.float32)
+        if dense is None and sg is None:
+            return u if u.dtype == self.act_dtype else ops.unary(u, None, self.act_dtype)
+        return ops.moe_scale(u, dense, experts=experts, ff=self.ff if experts else 1, shared_ff=shared_ff, shared_gate=sg, out_dtype=self.act_dtype,
+                             out=u if wide else None)
+
+    def forward(self, h: torch.Tensor, batch, logits: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """h: the layer input in the activation dtype; logits: the router's fp32 logits (and the shared gate's) when the caller has them
+        already. Returns fp32 [rows, width]."""
         E, rows = self.experts, h.shape[0]
-        z = self.router(h)
+        z = logits if logits is not None else self.router(h)
         sorted_form = batch.max_new > 1 and rows >= self.sorted_min_rows and (self.force_sorted or self._sorted_is_faster(rows))
-        idx, wt, dense = ops.moe_route(z, E, self.top, self.route_scale, dense=not sorted_form)
-        sg = z[:, E:E + 1] if self.shared_ff else None
+        idx, wt, dense = ops.moe_route(z, E, self.top, self.route_scale, dense=not sorted_form, kind=self.router_kind, groups=self.groups,
+                                       keep_groups=self.keep_groups, normalize=self.normalize)
+        sg = z[:, E:E + 1] if self.shared_gated else None
         if not sorted_form:
             # few rows: fp32 hidden activations, weighted, rounded once. Prompt-sized steps write them in the activation dtype from
             # the product's epilogue and weight them in place (half the bytes of the step's largest tensor, one more rounding)
             wide = rows > 32 and self.act_dtype != torch.float32
-            u = self.up_all(h, act=self.act, out_dtype=self.act_dtype if wide else torch.float32)
-            us = ops.moe_scale(u, dense, experts=E, ff=self.ff, shared_ff=self.shared_ff, shared_gate=sg, out_dtype=self.act_dtype,
-                               out=u if wide else None)
-            return self.down_all(us)
+            return self.down_all(self._hidden(self.up_all, h, dense, E, self.shared_ff, sg, wide))
         counts, offsets, perm, inv = ops.moe_sort(idx, E)
         xg = ops.moe_gather(h, perm, self.top, self.act_dtype)
         off = offsets.cpu().tolist()   # the one host decision of a prompt step: how many rows each expert got
@@ -389,11 +485,8 @@ class MoEFeedForward:
         for e in range(E):
             a, b = off[e], off[e + 1]
             if b > a:
-                u = self.up_e[e](xg[a:b], act=self.act, out_dtype=self.act_dtype)
-                self.down_e[e](u, out=part[a:b])
+                self.down_e[e](self._hidden(self.up_e[e], xg[a:b], None, 1, 0, None, True), out=part[a:b])
         ys = None
         if self.shared_ff:
-            u = self.up_s(h, act=self.act, out_dtype=torch.float32)
-            us = ops.moe_scale(u, None, experts=0, ff=1, shared_ff=self.shared_ff, shared_gate=sg, out_dtype=self.act_dtype)
-            ys = self.down_s(us)
+            ys = self.down_s(self._hidden(self.up_s, h, None, 0, self.shared_ff, sg, False))
         return ops.moe_combine(part, inv, wt, addend=ys)

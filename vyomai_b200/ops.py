@@ -971,11 +971,13 @@ def unary(x: torch.Tensor, act: Optional[str], out_dtype: torch.dtype, out: Opti
     return out
 
 
-def embed_rows(ids: torch.Tensor, table: torch.Tensor, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
-    _need_cuda(ids, table)
+def embed_rows(ids: torch.Tensor, table: torch.Tensor, scale: float, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(ids, table, out)
     if ids.dtype != torch.int32:
         raise _lib.VyomError("embed_rows: ids must be int32")
-    out = torch.empty((ids.numel(), table.shape[1]), device=table.device, dtype=out_dtype)
+    if out is None:
+        out = torch.empty((ids.numel(), table.shape[1]), device=table.device, dtype=out_dtype)
+    _rows2d(out, "embed_rows out")
     _lib.call_raw("vy_embed_rows", ids.numel(), table.shape[1], table.shape[0], ids.data_ptr(), table.data_ptr(), table.stride(0), _dt(table),
                   float(scale), out.data_ptr(), out.stride(0), _dt(out), _stream())
     return out
@@ -1045,8 +1047,14 @@ def rope_split(batch: PackedBatch, x: torch.Tensor, inv_freq: torch.Tensor, *, h
               rot_col=rot_col, rot_dtype=_dt(rot_out), stream=_stream(), **batch._kw(slots=False))
 
 
-def moe_route(logits: torch.Tensor, experts: int, top: int, scale: float, dense: bool = True):
-    """fp32 logits [rows, >= experts] -> (idx [rows, top] int32, weight [rows, top] fp32, dense [rows, experts] fp32 or None)."""
+ROUTE_KIND = {"sigmoid": C["VY_ROUTE_SIGMOID"], "softmax": C["VY_ROUTE_SOFTMAX"]}
+
+
+def moe_route(logits: torch.Tensor, experts: int, top: int, scale: float, dense: bool = True, kind: str = "sigmoid", groups: int = 0,
+              keep_groups: int = 0, normalize: bool = True):
+    """fp32 logits [rows, >= experts] -> (idx [rows, top] int32, weight [rows, top] fp32, dense [rows, experts] fp32 or None). kind: the
+    scores are sigmoids or the softmax over all experts; groups > 1: only members of the keep_groups best runs of neighbours are
+    eligible; normalize: the chosen scores are divided by their sum (else they are the weights as they are)."""
     _need_cuda(logits)
     _rows2d(logits, "moe_route logits")
     if logits.dtype != torch.float32:
@@ -1056,8 +1064,123 @@ def moe_route(logits: torch.Tensor, experts: int, top: int, scale: float, dense:
     wt = torch.empty((rows, top), device=logits.device, dtype=torch.float32)
     dn = torch.empty((rows, experts), device=logits.device, dtype=torch.float32) if dense else None
     _lib.call("vy_moe_route", "VyMoeRoute", rows=rows, experts=experts, top=top, logits=logits.data_ptr(), ld_logits=logits.stride(0),
-              scale=float(scale), idx=idx.data_ptr(), weight=wt.data_ptr(), dense=_ptr(dn), stream=_stream())
+              scale=float(scale), idx=idx.data_ptr(), weight=wt.data_ptr(), dense=_ptr(dn), stream=_stream(), kind=ROUTE_KIND[kind],
+              groups=int(groups), keep_groups=int(keep_groups), raw_weights=0 if normalize else 1)
     return idx, wt, dn
+
+
+def moe_glu(h: torch.Tensor, dense: Optional[torch.Tensor], *, experts: int, ff: int, shared_ff: int, limit: float, shared_limit: float = 0.0,
+            alpha: float = 1.702, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gated experts' activation over h [rows, experts * 2 ff + 2 shared_ff] (per expert [gate | up]): min(gate, limit) *
+    sigmoid(alpha * .) * (clamp(up, +-limit) + 1), times the routing weight dense[row, e] (None = 1); the shared block last, with its own
+    limit and weight 1. Returns [rows, experts * ff + shared_ff]."""
+    _need_cuda(h, dense, out)
+    _rows2d(h, "moe_glu h")
+    if h.shape[1] != 2 * (experts * ff + shared_ff):
+        raise _lib.VyomError(f"moe_glu: {h.shape[1]} columns, expected {2 * (experts * ff + shared_ff)}")
+    if out is None:
+        out = torch.empty((h.shape[0], _round_up(experts * ff + shared_ff, 8)), device=h.device, dtype=out_dtype)[:, :experts * ff + shared_ff]
+    _lib.call("vy_moe_glu", "VyMoeGlu", rows=h.shape[0], experts=experts, ff=ff, shared_ff=shared_ff, h=h.data_ptr(), ldh=h.stride(0), h_dtype=_dt(h),
+              dense=_ptr(dense), ld_dense=dense.stride(0) if dense is not None else 0, limit=float(limit), shared_limit=float(shared_limit),
+              alpha=float(alpha), out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
+    return out
+
+
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], *, eps: float, row_index: Optional[torch.Tensor] = None,
+               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Layer norm of packed rows (fp32 mean and mean squared deviation), optionally of the rows x[row_index]."""
+    _need_cuda(x, weight, bias, row_index)
+    _rows2d(x, "layer_norm x")
+    tokens = x.shape[0] if row_index is None else row_index.numel()
+    for t in (weight, bias):
+        if t is not None and (t.numel() != x.shape[1] or not t.is_contiguous()):
+            raise _lib.VyomError("layer_norm: weight and bias are contiguous [width]")
+    if weight is not None and bias is not None and weight.dtype != bias.dtype:
+        raise _lib.VyomError("layer_norm: weight and bias share a dtype")
+    out = torch.empty((tokens, x.shape[1]), device=x.device, dtype=out_dtype or x.dtype)
+    wd = weight if weight is not None else bias
+    _lib.call("vy_layer_norm", "VyLayerNorm", tokens=tokens, width=x.shape[1], row_index=_ptr(row_index), x=x.data_ptr(), ldx=x.stride(0),
+              x_dtype=_dt(x), weight=_ptr(weight), bias=_ptr(bias), w_dtype=_dt(wd) if wd is not None else 0, eps=float(eps), out=out.data_ptr(),
+              ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
+    return out
+
+
+def depth_mix(x: torch.Tensor, y1: torch.Tensor, g1: Optional[torch.Tensor], y2: Optional[torch.Tensor], g2: Optional[torch.Tensor], *,
+              stack: Optional[torch.Tensor] = None, depth: int = 0, coef: Optional[torch.Tensor] = None, mixed: Optional[torch.Tensor] = None,
+              norm_weight: Optional[torch.Tensor] = None, norm_bias: Optional[torch.Tensor] = None, eps: float = 0.0,
+              norm_out: Optional[torch.Tensor] = None) -> None:
+    """r = x + sigmoid(g1) * y1 + sigmoid(g2) * y2 (fp32; a missing gate is 1, y2 may be None). With `stack` [>= depth, rows, width] fp32,
+    r is stored as slice depth - 1 and mixed = sum_j coef[j] * stack[j] over the first `depth` slices; else mixed = r. `mixed` (fp32,
+    may be x) receives it; `norm_out` its layer norm."""
+    _need_cuda(x, y1, g1, y2, g2, stack, coef, mixed, norm_weight, norm_bias, norm_out)
+    for t, n in ((x, "x"), (y1, "y1"), (g1, "g1"), (y2, "y2"), (g2, "g2"), (mixed, "mixed"), (norm_out, "norm_out")):
+        if t is not None:
+            _rows2d(t, f"depth_mix {n}")
+    rows, width = x.shape
+    if x.dtype != torch.float32 or (mixed is not None and mixed.dtype != torch.float32):
+        raise _lib.VyomError("depth_mix: the residual is fp32")
+    kw = {}
+    if stack is not None:
+        if stack.dtype != torch.float32 or stack.dim() != 3 or stack.shape[0] < depth or tuple(stack.shape[1:]) != (rows, width) or not stack[0].is_contiguous() \
+                or coef is None or coef.dtype != torch.float32 or coef.numel() < depth:
+            raise _lib.VyomError("depth_mix: stack is fp32 [>= depth, rows, width] with contiguous slices, coef fp32 [>= depth]")
+        kw.update(stack=stack.data_ptr(), stack_stride=stack.stride(0), depth=int(depth), coef=coef.data_ptr())
+    if norm_out is not None:
+        wd = norm_weight if norm_weight is not None else norm_bias
+        kw.update(norm_weight=_ptr(norm_weight), norm_bias=_ptr(norm_bias), norm_w_dtype=_dt(wd) if wd is not None else 0, eps=float(eps),
+                  norm_out=norm_out.data_ptr(), ld_norm_out=norm_out.stride(0), norm_out_dtype=_dt(norm_out))
+    opt = lambda t, pre: {pre: t.data_ptr(), f"ld_{pre}": t.stride(0), f"{pre}_dtype": _dt(t)} if t is not None else {}  # noqa: E731
+    _lib.call("vy_depth_mix", "VyDepthMix", rows=rows, width=width, x=x.data_ptr(), ldx=x.stride(0), **opt(y1, "y1"), **opt(g1, "g1"), **opt(y2, "y2"),
+              **opt(g2, "g2"), mixed=_ptr(mixed), ld_mixed=mixed.stride(0) if mixed is not None else 0, stream=_stream(), **kw)
+
+
+def rope_kv_write(batch: PackedBatch, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: torch.Tensor, k_pool: torch.Tensor,
+                  v_pool: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int) -> None:
+    """Rotates q in place by position, rotates k into k_pool and copies v into v_pool at each token's page row (one launch)."""
+    _need_cuda(q, k, v, inv_freq, k_pool, v_pool)
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _rows2d(t, f"rope_kv_write {n}")
+    if not (q.dtype == k.dtype == v.dtype) or k_pool.dtype != v_pool.dtype or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+        raise _lib.VyomError("rope_kv_write: q / k / v and the two pools must share a dtype each; pools contiguous")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() < rot_dims // 2 or q.shape[1] < heads * dim or k.shape[1] < kv_heads * dim or v.shape[1] < kv_heads * vdim:
+        raise _lib.VyomError("rope_kv_write: inv_freq fp32 [rot_dims / 2]; q / k / v as wide as their heads")
+    _lib.call("vy_rope_kv_write", "VyRopeKvWrite", q=q.data_ptr(), ldq=q.stride(0), k=k.data_ptr(), ldk=k.stride(0), v=v.data_ptr(), ldv=v.stride(0),
+              in_dtype=_dt(q), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, rot_dims=rot_dims, inv_freq=inv_freq.data_ptr(),
+              k_pool=k_pool.data_ptr(), v_pool=v_pool.data_ptr(), pool_dtype=_dt(k_pool), stream=_stream(), **batch._kw(pages=True, slots=False))
+
+
+TALK_FORM = {None: 0, "rows": 1, "tiled": 2}
+
+
+def talk_attn(batch: PackedBatch, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int,
+              scale: float, softcap: float = 0.0, talk: Optional[torch.Tensor] = None, window: int = 0, sink: Optional[torch.Tensor] = None,
+              zero_sink: bool = False, gate: Optional[torch.Tensor] = None, gate_per_channel: bool = False, out_dtype: Optional[torch.dtype] = None,
+              form: Optional[str] = None) -> torch.Tensor:
+    """Causal attention over the paged pools (which already hold the step's keys) whose heads exchange scores before the softmax:
+    s_h = cap(q_h . k * scale), s_h <- sum_b talk[h, b] s_b, softmax with an optional sink term (a per-head score, or score 0), output
+    times a sigmoid gate per head or per channel. form: None = by the step's shape, "rows" / "tiled" force one."""
+    _need_cuda(q, k_pool, v_pool, talk, sink, gate)
+    _rows2d(q, "talk_attn q")
+    if talk is not None and (tuple(talk.shape) != (heads, heads) or not talk.is_contiguous()):
+        raise _lib.VyomError("talk_attn: talk is contiguous [heads, heads]")
+    if not (k_pool.is_contiguous() and v_pool.is_contiguous()) or k_pool.dtype != v_pool.dtype:
+        raise _lib.VyomError("talk_attn: pools contiguous, one dtype")
+    out = torch.empty((q.shape[0], heads * vdim), device=q.device, dtype=out_dtype or q.dtype)
+    tw = batch.block_table.shape[1] if batch.block_table is not None else 0
+    need = int(_lib.lib().vy_talk_attn_workspace_floats(batch.n_seqs, batch.max_new, tw, batch.block_size, heads, vdim)) if form != "tiled" else 0
+    ws = torch.empty(need, device=q.device, dtype=torch.float32) if need > 0 else None
+    _lib.call("vy_talk_attn", "VyTalkAttn", q=q.data_ptr(), ldq=q.stride(0), q_dtype=_dt(q), k_pool=k_pool.data_ptr(), v_pool=v_pool.data_ptr(),
+              pool_dtype=_dt(k_pool), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=float(scale), softcap=float(softcap), window=int(window),
+              talk=_ptr(talk), talk_dtype=_dt(talk) if talk is not None else 0, sink=_ptr(sink), sink_dtype=_dt(sink) if sink is not None else 0,
+              zero_sink=1 if zero_sink else 0, gate=_ptr(gate), ld_gate=gate.stride(0) if gate is not None else 0,
+              gate_dtype=_dt(gate) if gate is not None else 0, gate_per_channel=1 if gate_per_channel else 0, out=out.data_ptr(), ld_out=out.stride(0),
+              out_dtype=_dt(out), workspace=_ptr(ws), workspace_floats=need, force_form=TALK_FORM[form], stream=_stream(),
+              **batch._kw(pages=True, slots=False))
+    return out
 
 
 def moe_scale(h: torch.Tensor, dense: Optional[torch.Tensor], *, experts: int, ff: int, shared_ff: int, shared_gate: Optional[torch.Tensor],

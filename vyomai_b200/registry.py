@@ -37,6 +37,11 @@ def _zugunex(path, **kw):
     return ZugunexForCausalLM.from_pretrained(path, **kw)
 
 
+def _vazepel(path, **kw):
+    from .models.vazepel import VazepelForCausalLM
+    return VazepelForCausalLM.from_pretrained(path, **kw)
+
+
 def _custom_lm(path, dtype=torch.bfloat16, device=None, **kw):
     """The RMSNorm / SwiGLU / RoPE decoder (models/custom_transformer.py): config.json holds its Config fields, the checkpoint
     its state_dict."""
@@ -52,4 +57,5 @@ def _custom_lm(path, dtype=torch.bfloat16, device=None, **kw):
 
 register_model("Gelutar", _gelutar)
 register_model("Zugunex", _zugunex)
+register_model("Vazepel", _vazepel)
 register_model("ModelForCausalLM", _custom_lm)
