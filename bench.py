@@ -1104,10 +1104,11 @@ def latent_config(width, layers=8, vocab=32768, window=512):
             "layers": [{"type": "latent_attention", "mixer": mix(i), "mlp": {"kind": "dense", "ff": 4 * width} if i == 0 else moe} for i in range(layers)]}
 
 
-def _packed_numbers(dev, model, vocab, batch_prefill, prompt, batch_decode, decode_steps, steps, warmup):
+def _packed_numbers(dev, model, vocab, batch_prefill, prompt, batch_decode, decode_steps, steps, warmup, kernels=None):
     """Prefill and single-token-step timings of a packed-step model through HybridBatchEngine: prompts from pinned host ids inside the
     timed region with L2 flushed between iterations; decode as CUDA-graph replays; CUPTI kernel tables of one prefill and one eager step."""
     from vyomai_b200 import HybridBatchEngine, HybridCacheManager
+    kernels = kernels or LATENT_KERNELS
     g = torch.Generator().manual_seed(1)
     flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)
     mgr = HybridCacheManager(model, max_tokens=batch_decode * (prompt + decode_steps + 16), block_size=16, max_seqs=batch_decode)
@@ -1128,7 +1129,7 @@ def _packed_numbers(dev, model, vocab, batch_prefill, prompt, batch_decode, deco
             times.append(e0.elapsed_time(e1))
     pre_ms = sorted(times)[len(times) // 2]
     out["prefill"] = {"batch": batch_prefill, "prompt": prompt, "ms": round(pre_ms, 3), "tok_per_s": round(batch_prefill * prompt / pre_ms * 1e3)}
-    out["prefill_kernels"] = _kernel_table(lambda: prefill(batch_prefill), LATENT_KERNELS)
+    out["prefill_kernels"] = _kernel_table(lambda: prefill(batch_prefill), kernels)
     eng.release(range(batch_prefill))
     prefill(batch_decode)
     nxt = [[int(t)] for t in torch.randint(0, vocab, (batch_decode,), generator=g)]
@@ -1156,7 +1157,7 @@ def _packed_numbers(dev, model, vocab, batch_prefill, prompt, batch_decode, deco
                      "tok_per_s": round(batch_decode / step_us * 1e6), "graph": cap is not None}
     eng.use_graph = False
     one()
-    out["decode_kernels_eager"] = _kernel_table(one, LATENT_KERNELS)
+    out["decode_kernels_eager"] = _kernel_table(one, kernels)
     eng.release(range(batch_decode))
     return out
 
@@ -1252,6 +1253,117 @@ def run_latent(args):
                       "clocks": sampler.result(), "l2": "160 MB buffer rewritten between timed prefill iterations"}))
 
 
+# ------------------------------------------------------------------------------------------------
+# --workload talking: the Vazepel parallel-layer decoder (score-exchanging attention, gated experts) beside the Zugunex
+# latent-attention decoder at equal width / depth / vocabulary (both run on HybridBatchEngine's packed step)
+# ------------------------------------------------------------------------------------------------
+TALKING_KERNELS = ("talk_attn_tiled", "talk_attn_rows", "talk_attn_merge", "depth_mix_norm", "moe_glu", "rope_kv_write") + LATENT_KERNELS
+
+
+def talking_config(width, layers=8, vocab=32768):
+    """A realistic layer stack: heads of 64 query / key and 64 value channels, 4 query heads per key/value head, all channels rotated, a
+    dense tanh-GELU feed-forward (4 x width) in the first layer and 32 gated experts of width / 4 (4 chosen, 8 groups of which 4 are
+    kept) plus a shared expert of width / 2 in the others: the same expert sizes as latent_config()."""
+    H = width // 64
+    mix = {"heads": H, "kv_heads": max(H // 4, 1), "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0, "rot": {"base": 10000.0, "dims": 64}}
+    moe = {"kind": "moe", "expert": {"ff": width // 4, "limit": 7.0}, "router": {"experts": 32, "top": 4, "groups": {"count": 8, "keep": 4}},
+           "shared": {"ff": width // 2, "limit": 7.0}}
+    return {"architecture": "Vazepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": dict(mix), "mlp": {"kind": "dense", "ff": 4 * width} if i == 0 else moe} for i in range(layers)]}
+
+
+def talking_weights(model):
+    """Every weight a Vazepel decode step reads (the all-experts form reads every expert once)."""
+    seen = []
+    for L in model.layers:
+        seen += [L.inp.weight, L.mixer.o.weight]
+        if L.mlp is not None:
+            seen += [L.mlp.up_all.weight, L.mlp.down_all.weight] if L.moe else [L.mlp.up.weight, L.mlp.down.weight]
+    seen.append(model.head.weight)
+    return seen
+
+
+def measure_talking(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, decode_steps=64, steps=5, warmup=3):
+    from vyomai_b200 import VazepelConfig, VazepelForCausalLM, ZugunexConfig, ZugunexForCausalLM
+    hbm, _, _, src = peaks()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    fp32_tflops = sms * 128 * 2 * 1.965e9 / 1e12
+    cfgd = talking_config(width)
+    cfg = VazepelConfig(cfgd)
+    model = VazepelForCausalLM(cfg, VazepelForCausalLM.random_weights(cfg, seed=0), dtype=torch.bfloat16, device=dev)
+    out = {"width": width, "vocab": cfg.vocab, "peaks": src, "fp32_tflops_nominal": round(fp32_tflops, 1)}
+    z = _packed_numbers(dev, model, cfg.vocab, batch_prefill, prompt, batch_decode, decode_steps, steps, warmup, kernels=TALKING_KERNELS)
+    m = cfgd["layers"][0]["mixer"]
+    n_layers, H, G = len(cfgd["layers"]), m["heads"], m["kv_heads"]
+    tokens = batch_prefill * prompt
+    visible = (prompt + 1) / 2.0
+    # prompts: the two contractions (dim + vdim channels per query, key, head) plus the exchange (heads multiply-adds per query, key, head)
+    fl = n_layers * tokens * H * visible * (m["dim"] + m["vdim"] + H) * 2
+    ms = z["prefill_kernels"].get("talk_attn_tiled", {}).get("ms")
+    if ms:
+        z["talk_attn_tiled_roofline"] = {"gflop": round(fl / 1e9, 1), "tflops": round(fl / ms / 1e9, 2), "frac_of_fp32_nominal": round(fl / ms / 1e9 / fp32_tflops, 3)}
+    dk = z["decode_kernels_eager"]
+    ms = sum(dk.get(k, {}).get("ms", 0.0) for k in ("talk_attn_rows", "talk_attn_merge"))
+    if ms:
+        by = n_layers * batch_decode * prompt * G * (m["dim"] + m["vdim"]) * 4
+        dfl = n_layers * batch_decode * H * prompt * (m["dim"] + m["vdim"] + H) * 2
+        z["talk_attn_decode_roofline"] = {"MB_rows_once": round(by / 1e6, 1), "frac_of_hbm_rows_once": round(by / (ms * 1e-3) / 1e9 / hbm, 3),
+                                          "gflop": round(dfl / 1e9, 2), "tflops": round(dfl / ms / 1e9, 2),
+                                          "frac_of_fp32_nominal": round(dfl / ms / 1e9 / fp32_tflops, 3)}
+    step_bytes = 2.0 * sum(t.numel() for t in talking_weights(model)) + n_layers * batch_decode * prompt * G * (m["dim"] + m["vdim"]) * 4
+    if z["decode"]["us_per_step_device"]:
+        z["decode"].update(step_algorithmic_MB=round(step_bytes / 1e6, 1),
+                           hbm_frac_device=round(step_bytes / (z["decode"]["us_per_step_device"] * 1e-6) / 1e9 / hbm, 3))
+    out["vazepel"] = z
+    del model
+    torch.cuda.empty_cache()
+    # the closest existing model: latent attention over a 512-token window; its attention numbers as --workload latent derives them
+    ld = latent_config(width)
+    lcfg = ZugunexConfig(ld)
+    lmodel = ZugunexForCausalLM(lcfg, ZugunexForCausalLM.random_weights(lcfg, seed=0), dtype=torch.bfloat16, device=dev)
+    lz = _packed_numbers(dev, lmodel, lcfg.vocab, batch_prefill, prompt, batch_decode, decode_steps, steps, warmup)
+    lm = ld["layers"][0]["mixer"]
+    Wn = lm["mask"]["size"]
+    vis = sum(min(p + 1, Wn) for p in range(prompt)) / prompt
+    fl = len(ld["layers"]) * tokens * lm["heads"] * vis * (lm["dim"] + lm["rot_dim"] + lm["vdim"]) * 2
+    ms = lz["prefill_kernels"].get("window_attn_tiled", {}).get("ms")
+    if ms:
+        lz["window_attn_tiled_roofline"] = {"gflop": round(fl / 1e9, 1), "tflops": round(fl / ms / 1e9, 2), "frac_of_fp32_nominal": round(fl / ms / 1e9 / fp32_tflops, 3)}
+    dk = lz["decode_kernels_eager"]
+    ms = sum(dk.get(k, {}).get("ms", 0.0) for k in ("window_attn_heads", "window_attn_heads_merge", "window_attn_decode"))
+    if ms:
+        row = lm["kv_rank"] + lm["rot_dim"]
+        by = len(ld["layers"]) * batch_decode * min(Wn, prompt) * row * 4
+        dfl = len(ld["layers"]) * batch_decode * lm["heads"] * min(Wn, prompt) * (row + lm["kv_rank"]) * 2
+        lz["window_attn_decode_roofline"] = {"MB_rows_once": round(by / 1e6, 1), "frac_of_hbm_rows_once": round(by / (ms * 1e-3) / 1e9 / hbm, 3),
+                                             "gflop": round(dfl / 1e9, 2), "tflops": round(dfl / ms / 1e9, 2),
+                                             "frac_of_fp32_nominal": round(dfl / ms / 1e9 / fp32_tflops, 3)}
+    out["zugunex"] = lz
+    del lmodel
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_talking(args):
+    from vyomai_b200 import _lib
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus != 1:
+        print(json.dumps({"workload": "talking", "error": "the parallel-layer decoder measurement runs on one GPU"}))
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    L = _lib.lib()
+    sampler = ClockSampler(0)
+    sampler.start()
+    n0 = L.vy_launch_count()
+    res = [_guarded(measure_talking, dev, int(w), steps=max(args.steps // 2, 3), warmup=max(args.warmup, 3)) for w in args.hybrid_sizes.split(",")]
+    launches = L.vy_launch_count() - n0
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    print(json.dumps({"workload": "talking", "metric": "vazepel_prefill_and_decode_tokens_per_s", "n_gpus": 1, "dtype": "bf16 (fp32 residual / scores / router)",
+                      "data": "synthetic", "sizes": res, "gpu_launches_total": int(launches), "gemm_poisoned": int(L.vy_gemm_poisoned()),
+                      "clocks": sampler.result(), "l2": "160 MB buffer rewritten between timed prefill iterations"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1259,13 +1371,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="package", choices=["package", "slots", "hybrid", "latent"],
+    ap.add_argument("--workload", default="package", choices=["package", "slots", "hybrid", "latent", "talking"],
                     help="package: VisionLanguageModel of the reference package (1 image token + 127 text, the headline); "
                          "slots: the notebook-II form (197 image tokens in a 248-token sequence); "
                          "hybrid: prefill / decode throughput of the Gelutar hybrid decoder beside DecoderModel at equal size (1 GPU, "
                          "its own JSON line; not the headline metric); "
-                         "latent: the same for the Zugunex latent-attention / mixture-of-experts decoder beside Gelutar at equal size")
-    ap.add_argument("--hybrid-sizes", default="1024,2048", help="--workload hybrid / latent: model widths to measure")
+                         "latent: the same for the Zugunex latent-attention / mixture-of-experts decoder beside Gelutar at equal size; "
+                         "talking: the same for the Vazepel parallel-layer decoder (score-exchanging attention heads) beside Zugunex")
+    ap.add_argument("--hybrid-sizes", default="1024,2048", help="--workload hybrid / latent / talking: model widths to measure")
     ap.add_argument("--no-configs-1-2", action="store_true", help="skip the encoder (C1) / ViT (C2) measurements appended at N = 1")
     ap.add_argument("--no-config5", action="store_true", help="skip the PaliGemma-scale prefill + decode measurement appended at N = 1")
     ap.add_argument("--no-slots", action="store_true", help="skip the notebook-II measurement appended at N = 1")
@@ -1284,6 +1397,8 @@ def main():
         run_hybrid(args)
     elif args.workload == "latent":
         run_latent(args)
+    elif args.workload == "talking":
+        run_talking(args)
     else:
         run_ours(args)
 
