@@ -196,7 +196,8 @@ def _run_attn(m, q, k, v, talk, gate, steps, form, bs=4):
 
 @pytest.mark.parametrize("form", ["rows", "tiled"])
 @pytest.mark.parametrize("shape", [dict(heads=6, kv_heads=3, dim=10, vdim=7), dict(heads=8, kv_heads=2, dim=32, vdim=24), dict(heads=3, kv_heads=1, dim=6, vdim=70),
-                                   dict(heads=24, kv_heads=4, dim=12, vdim=72), dict(heads=5, kv_heads=5, dim=4, vdim=3)])
+                                   dict(heads=24, kv_heads=4, dim=12, vdim=72), dict(heads=5, kv_heads=5, dim=4, vdim=3), dict(heads=40, kv_heads=8, dim=8, vdim=6),
+                                   dict(heads=16, kv_heads=4, dim=64, vdim=64)])
 @pytest.mark.parametrize("steps", [[75], [40, 1, 1, 33], [2] * 37 + [1]])
 def test_score_exchanging_attention(form, shape, steps):
     m = U.attn(scale=0.4, softcap=3.0, **shape)

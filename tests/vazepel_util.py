@@ -56,9 +56,11 @@ def aligned_config(width=128) -> dict:
 
 def wide_config() -> dict:
     """Heads and channels beyond one 64-row block of the tiled attention: 24 heads (two blocks of rows), 72 value channels (two column
-    passes), and 40 heads (the tiled form does not apply: every step takes the one-query form)."""
+    passes), 40 heads (four blocks), and 72 heads or 136 value channels (the tiled form does not apply: every step takes the one-query
+    form)."""
     return config([layer(attn(heads=24, kv_heads=4, dim=12, vdim=72, rot_dims=8), dense(ff=48)),
                    layer(attn(heads=40, kv_heads=8, dim=8, vdim=6), None),
+                   layer(attn(heads=72, kv_heads=8, dim=8, vdim=6), None),
                    layer(attn(heads=16, kv_heads=8, dim=20, vdim=136, rot_dims=20), dense(ff=32))], width=48, vocab=101)
 
 

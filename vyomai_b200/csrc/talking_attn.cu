@@ -32,13 +32,26 @@ struct TalkDev {
   void* out; long long ld_out; int out_dt;
 };
 
-__device__ __forceinline__ float cap_score(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+// cap * tanh(s / cap) as cap * (1 - 2 / (1 + e^(2 s / cap))): expf and a fast reciprocal, absolute error a few 1e-7 * cap (the softmax
+// that follows depends on score differences, i.e. on absolute error); e^x overflowing to inf gives exactly cap, underflow exactly -cap
+__device__ __forceinline__ float cap_score(float s, float cap, float two_over_cap) {
+  return cap > 0.f ? cap * (1.f - __fdividef(2.f, 1.f + expf(s * two_over_cap))) : s;
+}
 
 // the extra softmax term of head h as (score, present)
 __device__ __forceinline__ bool sink_of(const TalkDev& d, int h, float& s) {
   if (d.sink) { s = ld_as_float(d.sink, d.sink_dt, h); return true; }
   s = 0.f;
   return d.zero_sink != 0;
+}
+
+// talk[h, b] -> T_s[b * Hp + h], zero for the padding heads; identity without a matrix
+template <int T>
+__device__ __forceinline__ void load_talk(const TalkDev& d, float* T_s, int H, int Hp) {
+  for (int e = threadIdx.x; e < H * Hp; e += T) {
+    const int b = e / Hp, h = e - b * Hp;
+    T_s[e] = h >= H ? 0.f : (d.talk ? ld_as_float(d.talk, d.talk_dt, h * H + b) : (h == b ? 1.f : 0.f));
+  }
 }
 
 __device__ __forceinline__ float gate_of(const TalkDev& d, long long row, int h, int c) {
@@ -51,18 +64,18 @@ constexpr int TR_T = 256;   // threads
 constexpr int TR_N = 64;    // keys per tile
 
 // grid (token of the sequence, sequence, split). Shared memory (floats): q [H][dim4] | staged rows [TR_N][ld_s] | S [H][TR_N] |
-// P [H][TR_N] | talk [H][H] | m, l, corr [H] each | acc [H][vdim] | key rows (int) [TR_N].
+// P [H][TR_N] | talk transposed [H][Hp] (Hp = H rounded up to 4, zero padded) | m, l, corr [H] each | acc [H][vdim] | key rows (int) [TR_N].
 __global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim4, int vdim4, int ld_s, bool qvec, bool kvvec, int splits, float* ws) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) float tr_smem[];
-  const int H = d.heads, G = d.kv_heads, per = H / G;
+  const int H = d.heads, G = d.kv_heads, per = H / G, Hp = (H + 3) & ~3;
   float* q_s = tr_smem;
   float* kv_s = q_s + H * dim4;
   float* S_s = kv_s + TR_N * ld_s;
   float* P_s = S_s + H * TR_N;
-  float* T_s = P_s + H * TR_N;
-  float* m_s = T_s + H * H;
+  float* T_s = P_s + H * TR_N;          // T_s[b * Hp + h] = talk[h, b]
+  float* m_s = T_s + H * Hp;
   float* l_s = m_s + H;
   float* c_s = l_s + H;
   float* acc_s = c_s + H;
@@ -79,10 +92,11 @@ __global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim
   const int tps = (tiles + splits - 1) / splits;
   const int tile0 = split * tps, tile1 = min(tiles, tile0 + tps);
   const int* tab = d.table + static_cast<long long>(s) * d.tw;
+  const float two_over_cap = d.softcap > 0.f ? 2.f / d.softcap : 0.f;
 
   rows_to_smem<TR_T>(q_s, dim4, H, d.dim, dim4, d.q, d.q_dt, qvec, VY_UACT_NONE,
                      [&](int h) { return qrow * d.ldq + static_cast<long long>(h) * d.dim; });
-  for (int e = t; e < H * H; e += TR_T) T_s[e] = d.talk ? ld_as_float(d.talk, d.talk_dt, e) : (e / H == e % H ? 1.f : 0.f);
+  load_talk<TR_T>(d, T_s, H, Hp);
   for (int h = t; h < H; h += TR_T) {
     float sk;
     const bool has = splits == 1 && sink_of(d, h, sk);   // with splits the merge adds the sink
@@ -110,15 +124,24 @@ __global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim
         const float* kp = kv_s + j * ld_s;
         float a = 0.f;
         for (int c = 0; c < dim4; c += 4) a = dot4(f4(qp + c), f4(kp + c), a);
-        S_s[h * TR_N + j] = cap_score(a * d.scale, d.softcap);
+        S_s[h * TR_N + j] = cap_score(a * d.scale, d.softcap, two_over_cap);
       }
     }
     __syncthreads();
-    for (int it = t; it < H * TR_N; it += TR_T) {
-      const int h = it / TR_N, j = it - h * TR_N;
-      float a = 0.f;
-      for (int b = 0; b < H; ++b) a = fmaf(T_s[h * H + b], S_s[b * TR_N + j], a);
-      P_s[it] = j < nk ? a : -INFINITY;
+    for (int it = t; it < (Hp >> 2) * TR_N; it += TR_T) {   // 4 receiving heads of one key per thread
+      const int hq = it / TR_N, j = it - hq * TR_N;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int b = 0; b < H; ++b) {
+        const float4 w = f4(T_s + b * Hp + 4 * hq);
+        const float x = S_s[b * TR_N + j];
+        a.x = fmaf(w.x, x, a.x); a.y = fmaf(w.y, x, a.y); a.z = fmaf(w.z, x, a.z); a.w = fmaf(w.w, x, a.w);
+      }
+      const bool live = j < nk;
+      const int h0 = 4 * hq;
+      P_s[h0 * TR_N + j] = live ? a.x : -INFINITY;
+      if (h0 + 1 < H) P_s[(h0 + 1) * TR_N + j] = live ? a.y : -INFINITY;
+      if (h0 + 2 < H) P_s[(h0 + 2) * TR_N + j] = live ? a.z : -INFINITY;
+      if (h0 + 3 < H) P_s[(h0 + 3) * TR_N + j] = live ? a.w : -INFINITY;
     }
     __syncthreads();
     for (int h = warp; h < H; h += TR_T / 32) {
@@ -169,29 +192,31 @@ __global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim
   }
 }
 
-// one CTA per row: combines the splits' parts, adds the sink term, gates and stores
-__global__ void __launch_bounds__(128) talk_attn_merge_kernel(TalkDev d, int rows, int splits, const float* ws) {
+// one CTA per (row, head): combines the splits' parts, adds the sink term, gates and stores
+__global__ void __launch_bounds__(64) talk_attn_merge_kernel(TalkDev d, int splits, const float* ws) {
   pdl_trigger();
   pdl_wait();
   const long long row = blockIdx.x;
-  const int H = d.heads;
-  const float* w0 = ws + row * splits * static_cast<long long>(H) * (d.vdim + 2);
+  const int H = d.heads, h = blockIdx.y;
   const long long part = static_cast<long long>(H) * (d.vdim + 2);
-  for (int o = threadIdx.x; o < H * d.vdim; o += blockDim.x) {
-    const int h = o / d.vdim, c = o - h * d.vdim;
-    float sk;
-    const bool has = sink_of(d, h, sk);
-    float m = has ? sk : -INFINITY;
-    for (int k = 0; k < splits; ++k) m = fmaxf(m, w0[k * part + h]);
-    float l = has ? expf(sk - m) : 0.f, a = 0.f;
+  const float* w0 = ws + row * splits * part;
+  float sk;
+  const bool has = sink_of(d, h, sk);
+  float m = has ? sk : -INFINITY;
+  for (int k = 0; k < splits; ++k) m = fmaxf(m, w0[k * part + h]);
+  float l = has ? expf(sk - m) : 0.f;
+  for (int k = 0; k < splits; ++k) {
+    const float mk = w0[k * part + h];
+    if (mk != -INFINITY) l = fmaf(w0[k * part + H + h], expf(mk - m), l);
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int c = threadIdx.x; c < d.vdim; c += blockDim.x) {
+    float a = 0.f;
     for (int k = 0; k < splits; ++k) {
       const float mk = w0[k * part + h];
-      if (mk == -INFINITY) continue;
-      const float f = expf(mk - m);
-      l = fmaf(w0[k * part + H + h], f, l);
-      a = fmaf(w0[k * part + 2 * H + o], f, a);
+      if (mk != -INFINITY) a = fmaf(w0[k * part + 2 * H + h * d.vdim + c], expf(mk - m), a);
     }
-    st_from_float(d.out, d.out_dt, row * d.ld_out + o, l > 0.f ? a / l * gate_of(d, row, h, c) : 0.f);
+    st_from_float(d.out, d.out_dt, row * d.ld_out + static_cast<long long>(h) * d.vdim + c, a * inv * gate_of(d, row, h, c));
   }
 }
 
@@ -201,24 +226,24 @@ __global__ void __launch_bounds__(128) talk_attn_merge_kernel(TalkDev d, int row
 // columns 4 (tj + 16 mm) .. + 3 of those rows in the output phase. Per key tile: the key rows of every key/value head go to
 // shared memory ([kv head][key][channel]), each thread contracts its rows with its head's keys, the exchange reads every head's raw
 // scores, the online softmax runs by warps over rows, then the value rows replace the keys and are accumulated.
-constexpr int TT_T = 256;
-
-template <int RB, int MV, int KN>   // KN keys per tile: 32, or 16 when many wide key/value heads would not fit otherwise
-__global__ void __launch_bounds__(TT_T, RB == 1 ? 2 : 1)
+// NT threads (256, or 512 for 256 rows: two CTAs' worth of warps on one staged key tile); a pass of the thread grid covers NT / 4 rows.
+template <int NT, int RB, int MV, int KN>   // KN keys per tile: 32, or 16 when many wide key/value heads would not fit otherwise
+__global__ void __launch_bounds__(NT, (NT == 256 && RB * MV <= 2) ? 2 : 1)
 talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ldkv, bool qvec, bool kvvec) {
   pdl_trigger();
   pdl_wait();
-  constexpr int R = 64 * RB, LDP = KN + 4, NCB = KN / 16;
+  constexpr int TT_T = NT, PASS = NT / 4, R = PASS * RB, LDP = KN + 4, NCB = KN / 16;
   extern __shared__ __align__(16) float tt_smem[];
-  const int H = d.heads, G = d.kv_heads, per = H / G;
+  const int H = d.heads, G = d.kv_heads, per = H / G, Hp = (H + 3) & ~3;
   float* Q_s = tt_smem;                    // [R][ldq_s]
   float* K_s = Q_s + R * ldq_s;            // [G][KN][ldkv]  (keys, then values)
   float* S_s = K_s + G * KN * ldkv;        // [R][LDP] raw scores
   float* P_s = S_s + R * LDP;              // [R][LDP] mixed scores, then weights
-  float* T_s = P_s + R * LDP;              // [H][H]
-  float* corr_s = T_s + H * H;             // [R]
-  float* l_out = corr_s + R;               // [R]
-  int* krow_s = reinterpret_cast<int*>(l_out + R);   // [KN]
+  float* T_s = P_s + R * LDP;              // [H][Hp]: T_s[b * Hp + h] = talk[h, b]
+  float* corr_s = T_s + H * Hp;            // [R]
+  float* m_s = corr_s + R;                 // [R] running maximum
+  float* l_s = m_s + R;                    // [R] running sum
+  int* krow_s = reinterpret_cast<int*>(l_s + R);   // [KN]
   const int s = blockIdx.y, i0 = blockIdx.x * TQ;
   const int t = threadIdx.x, ti = t >> 4, tj = t & 15, warp = t >> 5, lane = t & 31;
   const int base = d.cu[s], n = d.cu[s + 1] - base;
@@ -229,26 +254,23 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
     const int h = r / TQ, i = r - h * TQ;
     return (r < rows && i < nq) ? static_cast<long long>(base + i0 + i) * d.ldq + static_cast<long long>(h) * d.dim : -1LL;
   });
-  for (int e = t; e < H * H; e += TT_T) T_s[e] = d.talk ? ld_as_float(d.talk, d.talk_dt, e) : (e / H == e % H ? 1.f : 0.f);
+  load_talk<TT_T>(d, T_s, H, Hp);
   const int p_lo = d.pos0[s] + i0, p_hi = p_lo + nq - 1;
   const int lo = d.window > 0 ? max(p_lo - d.window + 1, 0) : 0;
   const int count = p_hi - lo + 1;
   const int* tab = d.table + static_cast<long long>(s) * d.tw;
-  constexpr int RPW = R / 8;   // rows per warp in the softmax phase
-  float m[RPW], l[RPW];
-#pragma unroll
-  for (int rr = 0; rr < RPW; ++rr) {
-    const int r = warp * RPW + rr;
+  const float two_over_cap = d.softcap > 0.f ? 2.f / d.softcap : 0.f;
+  for (int r = t; r < R; r += TT_T) {
     float sk;
     const bool has = r < rows && sink_of(d, r / TQ, sk);
-    m[rr] = has ? sk : -INFINITY;
-    l[rr] = has ? 1.f : 0.f;
+    m_s[r] = has ? sk : -INFINITY;
+    l_s[r] = has ? 1.f : 0.f;
   }
   float acc[RB][4][MV][4];
   int kvoff[RB];   // this thread's rows read the staged rows of their key/value head: K_s + kvoff
 #pragma unroll
   for (int b = 0; b < RB; ++b) {
-    const int r0 = 64 * b + 4 * ti;
+    const int r0 = PASS * b + 4 * ti;
     kvoff[b] = r0 < rows ? (r0 / TQ / per) * KN * ldkv : -1;
 #pragma unroll
     for (int r = 0; r < 4; ++r)
@@ -275,7 +297,7 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
 #pragma unroll
     for (int b = 0; b < RB; ++b) {
       if (kvoff[b] < 0) continue;
-      const int r0 = 64 * b + 4 * ti;
+      const int r0 = PASS * b + 4 * ti;
       const float* Kg = K_s + kvoff[b];
       float sc[4][NCB];
 #pragma unroll
@@ -297,7 +319,7 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
 #pragma unroll
       for (int r = 0; r < 4; ++r)
 #pragma unroll
-        for (int cb = 0; cb < NCB; ++cb) S_s[(r0 + r) * LDP + tj + 16 * cb] = cap_score(sc[r][cb] * d.scale, d.softcap);
+        for (int cb = 0; cb < NCB; ++cb) S_s[(r0 + r) * LDP + tj + 16 * cb] = cap_score(sc[r][cb] * d.scale, d.softcap, two_over_cap);
     }
     __syncthreads();
     // values replace the keys while the exchange and the softmax run from S_s / P_s
@@ -306,37 +328,70 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
       return krow_s[j] >= 0 ? (static_cast<long long>(krow_s[j]) * G + g) * d.vdim : -1LL;
     });
     // exchange + mask: element (h, i, j) of P = sum_b talk[h, b] S[b, i, j]
-    for (int it = t; it < rows * (KN / 4); it += TT_T) {
-      const int r = it / (KN / 4), j4 = (it - r * (KN / 4)) * 4;
-      const int h = r / TQ, i = r - h * TQ;
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    // each thread: 4 receiving heads x one query x 4 keys, reading every head's raw scores of that (query, keys) once
+    for (int it = t; it < (Hp >> 2) * TQ * (KN / 4); it += TT_T) {
+      const int j4 = (it % (KN / 4)) * 4, hi = it / (KN / 4);
+      const int i = hi % TQ, hq = hi / TQ;
+      float4 a[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) a[k] = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int b = 0; b < H; ++b) {
-        const float w = T_s[h * H + b];
+        const float4 w = f4(T_s + b * Hp + 4 * hq);
         const float4 x = f4(S_s + (b * TQ + i) * LDP + j4);
-        a.x = fmaf(w, x.x, a.x); a.y = fmaf(w, x.y, a.y); a.z = fmaf(w, x.z, a.z); a.w = fmaf(w, x.w, a.w);
+        a[0].x = fmaf(w.x, x.x, a[0].x); a[0].y = fmaf(w.x, x.y, a[0].y); a[0].z = fmaf(w.x, x.z, a[0].z); a[0].w = fmaf(w.x, x.w, a[0].w);
+        a[1].x = fmaf(w.y, x.x, a[1].x); a[1].y = fmaf(w.y, x.y, a[1].y); a[1].z = fmaf(w.y, x.z, a[1].z); a[1].w = fmaf(w.y, x.w, a[1].w);
+        a[2].x = fmaf(w.z, x.x, a[2].x); a[2].y = fmaf(w.z, x.y, a[2].y); a[2].z = fmaf(w.z, x.z, a[2].z); a[2].w = fmaf(w.z, x.w, a[2].w);
+        a[3].x = fmaf(w.w, x.x, a[3].x); a[3].y = fmaf(w.w, x.y, a[3].y); a[3].z = fmaf(w.w, x.z, a[3].z); a[3].w = fmaf(w.w, x.w, a[3].w);
       }
       const int pq = p_lo + i, kp0 = lo + c0 + j4;
       const bool live = i < nq;
-      float* pr = P_s + r * LDP + j4;
       const auto vis = [&](int kp, int j) { return live && j < nk && kp <= pq && (d.window <= 0 || pq - kp < d.window); };
-      pr[0] = vis(kp0, j4) ? a.x : -INFINITY;
-      pr[1] = vis(kp0 + 1, j4 + 1) ? a.y : -INFINITY;
-      pr[2] = vis(kp0 + 2, j4 + 2) ? a.z : -INFINITY;
-      pr[3] = vis(kp0 + 3, j4 + 3) ? a.w : -INFINITY;
+      const bool v0 = vis(kp0, j4), v1 = vis(kp0 + 1, j4 + 1), v2 = vis(kp0 + 2, j4 + 2), v3 = vis(kp0 + 3, j4 + 3);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int h = 4 * hq + k;
+        if (h < H)
+          *reinterpret_cast<float4*>(P_s + (h * TQ + i) * LDP + j4) =
+              make_float4(v0 ? a[k].x : -INFINITY, v1 ? a[k].y : -INFINITY, v2 ? a[k].z : -INFINITY, v3 ? a[k].w : -INFINITY);
+      }
     }
     __syncthreads();
+    // online softmax: two adjacent lanes own a row (KN / 2 keys each, 16-byte accesses), one exchange for the maximum and one for the sum
+    for (int rb = warp * 16; rb < rows; rb += TT_T / 2) {   // warp-uniform bound: every lane takes part in the exchanges
+      constexpr int HK = KN / 2;
+      const int r = rb + (lane >> 1);
+      const bool live = r < rows;
+      float* pr = P_s + (live ? r : rb) * LDP + (t & 1) * HK;
+      float x[HK];
 #pragma unroll
-    for (int rr = 0; rr < RPW; ++rr) {
-      const int r = warp * RPW + rr;
-      float* pr = P_s + r * LDP;
-      const float a = (r < rows && lane < KN) ? pr[lane] : -INFINITY;
-      const float mn = fmaxf(m[rr], warp_max(a));
-      const float cr = mn == -INFINITY ? 1.f : expf(m[rr] - mn);
-      const float pa = a == -INFINITY ? 0.f : expf(a - mn);
-      if (lane < KN) pr[lane] = pa;
-      l[rr] = fmaf(l[rr], cr, warp_sum(pa));
-      m[rr] = mn;
-      if (lane == 0) corr_s[r] = cr;
+      for (int k = 0; k < HK; k += 4) {
+        const float4 v = f4(pr + k);
+        x[k] = v.x; x[k + 1] = v.y; x[k + 2] = v.z; x[k + 3] = v.w;
+      }
+      float mx = x[0];
+#pragma unroll
+      for (int k = 1; k < HK; ++k) mx = fmaxf(mx, x[k]);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      const float mo = m_s[live ? r : rb];
+      const float mn = fmaxf(mo, mx);
+      const float cr = mn == -INFINITY ? 1.f : expf(mo - mn);
+      float sum = 0.f;
+#pragma unroll
+      for (int k = 0; k < HK; ++k) {
+        x[k] = x[k] == -INFINITY ? 0.f : expf(x[k] - mn);
+        sum += x[k];
+      }
+      if (live) {
+#pragma unroll
+        for (int k = 0; k < HK; k += 4) *reinterpret_cast<float4*>(pr + k) = make_float4(x[k], x[k + 1], x[k + 2], x[k + 3]);
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      __syncwarp();   // both lanes have read m_s[r] before it changes
+      if (live && (t & 1) == 0) {
+        l_s[r] = fmaf(l_s[r], cr, sum);
+        m_s[r] = mn;
+        corr_s[r] = cr;
+      }
     }
     __syncthreads();
     // values
@@ -344,7 +399,7 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
 #pragma unroll
     for (int b = 0; b < RB; ++b) {
       if (kvoff[b] < 0) continue;
-      const int r0 = 64 * b + 4 * ti;
+      const int r0 = PASS * b + 4 * ti;
       const float* Vg = K_s + kvoff[b];
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
@@ -377,21 +432,16 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
     }
   }
   __syncthreads();
-  if (lane == 0) {
-#pragma unroll
-    for (int rr = 0; rr < RPW; ++rr) l_out[warp * RPW + rr] = l[rr];
-  }
-  __syncthreads();
 #pragma unroll
   for (int b = 0; b < RB; ++b)
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const int row = 64 * b + 4 * ti + r;
+      const int row = PASS * b + 4 * ti + r;
       if (row >= rows) continue;
       const int h = row / TQ, i = row - h * TQ;
       if (i >= nq) continue;
       const long long qrow = base + i0 + i;
-      const float lv = l_out[row];
+      const float lv = l_s[row];
       const float inv = lv > 0.f ? 1.f / lv : 0.f;
 #pragma unroll
       for (int mm = 0; mm < MV; ++mm)
@@ -406,11 +456,11 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
 
 // ---- host side ----------------------------------------------------------------------------------------------------------------
 static int rows_splits(int n_seqs, int max_new, int table_width, int block_size) {
-  // single-token steps only: enough CTAs for two waves of the SMs, at most one per key tile, at most 64
+  // single-token steps only: enough CTAs for four per SM (the latency of a tile's loads is hidden by other CTAs), at most one per key tile, at most 64
   if (max_new != 1) return 1;
   const long long rows = static_cast<long long>(n_seqs) * max_new;
   const long long max_tiles = (static_cast<long long>(table_width) * block_size + TR_N - 1) / TR_N;
-  long long want = (2 * 148 + rows - 1) / rows;
+  long long want = (4 * 148 + rows - 1) / rows;
   if (want > max_tiles) want = max_tiles;
   if (want > 64) want = 64;
   return want < 1 ? 1 : static_cast<int>(want);
@@ -418,48 +468,55 @@ static int rows_splits(int n_seqs, int max_new, int table_width, int block_size)
 
 static size_t rows_smem(const TalkDev& d, int dim4, int ld_s) {
   const size_t H = d.heads;
-  return sizeof(float) * (H * dim4 + static_cast<size_t>(TR_N) * ld_s + 2 * H * TR_N + H * H + 3 * H + H * d.vdim) + sizeof(int) * TR_N;
+  return sizeof(float) * (H * dim4 + static_cast<size_t>(TR_N) * ld_s + 2 * H * TR_N + H * ((H + 3) & ~3) + 3 * H + H * d.vdim) + sizeof(int) * TR_N;
 }
 
 static int pad_ld(int w4) { return ((w4 >> 2) & 1) ? w4 + 8 : w4 + 4; }   // (row stride / 4) odd: rows 1 apart start in distinct 16-byte bank groups
 
-struct TiledPlan { int RB, MV, KN, TQ, ldq_s, ldkv; size_t smem; bool ok; };
+struct TiledPlan { int NT, RB, MV, KN, TQ, ldq_s, ldkv; size_t smem; bool ok; };
 
 static TiledPlan tiled_plan(const TalkDev& d, int dim4, int vdim4) {
   TiledPlan pl;
   memset(&pl, 0, sizeof(pl));
   const int H = d.heads;
-  if (H * 4 > 128 || d.vdim > 128) return pl;
+  if (d.vdim > 128) return pl;
   pl.MV = d.vdim <= 64 ? 1 : 2;
-  pl.RB = H * 4 <= 64 ? 1 : 2;
-  const int R = 64 * pl.RB;
+  // rows per CTA: 64, 128 (256 threads) or 256 (512 threads, each still owning two 4-row blocks): as few as give every head 8 queries
+  // per tile, so that each staged key row serves 8 queries of every head of its group
+  static const int rows_env = getenv("VY_TALK_ATTN_ROWS") ? atoi(getenv("VY_TALK_ATTN_ROWS")) : 0;   // development: 64, 128 or 256
+  if (H * 4 > 256) return pl;
+  int R = 64;
+  while (R < 256 && (R / H < 8 || H * 4 > R)) R *= 2;
+  if ((rows_env == 64 || rows_env == 128 || rows_env == 256) && H * 4 <= rows_env) R = rows_env;
+  pl.NT = R == 256 ? 512 : 256;
+  pl.RB = R / (pl.NT / 4);
   pl.TQ = (R / H) & ~3;   // queries per tile: a multiple of 4, so the 4 rows of a thread share a head
   pl.ldq_s = pad_ld(dim4);
   pl.ldkv = pad_ld(dim4 > vdim4 ? dim4 : vdim4);
   for (pl.KN = 32; pl.KN >= 16; pl.KN >>= 1) {
     pl.smem = sizeof(float) * (static_cast<size_t>(R) * pl.ldq_s + static_cast<size_t>(d.kv_heads) * pl.KN * pl.ldkv + 2 * static_cast<size_t>(R) * (pl.KN + 4) +
-                               static_cast<size_t>(H) * H + 2 * R) + sizeof(int) * pl.KN;
+                               static_cast<size_t>(H) * ((H + 3) & ~3) + 3 * R) + sizeof(int) * pl.KN;
     // 32-key tiles when two CTAs fit an SM with them or nothing smaller is needed; 16-key tiles when 32 do not fit at all
     if (pl.smem <= 200 * 1024) { pl.ok = true; break; }
   }
   return pl;
 }
 
-template <int RB, int MV, int KN>
+template <int NT, int RB, int MV, int KN>
 static cudaError_t launch_tiled_kn(const TalkDev& d, const TiledPlan& pl, int n_seqs, int max_new, int dim4, int vdim4, bool qvec, bool kvvec, cudaStream_t st) {
   static size_t allowed = 48 * 1024;
   if (pl.smem > allowed) {
-    cudaError_t e = cudaFuncSetAttribute(talk_attn_tiled_kernel<RB, MV, KN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem));
+    cudaError_t e = cudaFuncSetAttribute(talk_attn_tiled_kernel<NT, RB, MV, KN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem));
     if (e != cudaSuccess) return e;
     allowed = pl.smem;
   }
-  return launch_kernel(talk_attn_tiled_kernel<RB, MV, KN>, dim3((max_new + pl.TQ - 1) / pl.TQ, n_seqs), dim3(TT_T), pl.smem, st, d, pl.TQ, dim4, vdim4,
+  return launch_kernel(talk_attn_tiled_kernel<NT, RB, MV, KN>, dim3((max_new + pl.TQ - 1) / pl.TQ, n_seqs), dim3(NT), pl.smem, st, d, pl.TQ, dim4, vdim4,
                        pl.ldq_s, pl.ldkv, qvec, kvvec);
 }
-template <int RB, int MV>
+template <int NT, int RB, int MV>
 static cudaError_t launch_tiled(const TalkDev& d, const TiledPlan& pl, int n_seqs, int max_new, int dim4, int vdim4, bool qvec, bool kvvec, cudaStream_t st) {
-  return pl.KN == 32 ? launch_tiled_kn<RB, MV, 32>(d, pl, n_seqs, max_new, dim4, vdim4, qvec, kvvec, st)
-                     : launch_tiled_kn<RB, MV, 16>(d, pl, n_seqs, max_new, dim4, vdim4, qvec, kvvec, st);
+  return pl.KN == 32 ? launch_tiled_kn<NT, RB, MV, 32>(d, pl, n_seqs, max_new, dim4, vdim4, qvec, kvvec, st)
+                     : launch_tiled_kn<NT, RB, MV, 16>(d, pl, n_seqs, max_new, dim4, vdim4, qvec, kvvec, st);
 }
 
 }  // namespace vy
@@ -504,14 +561,16 @@ extern "C" int vy_talk_attn(const VyTalkAttn* p) {
   const bool qvec = d.q_dt == VY_F32 && d.dim % 4 == 0 && d.ldq % 4 == 0 && al(d.q);
   const bool kvvec = d.pool_dt == VY_F32 && d.dim % 4 == 0 && d.vdim % 4 == 0 && al(d.kp) && al(d.vp);
   const TiledPlan pl = tiled_plan(d, dim4, vdim4);
-  VY_CHECK_ARG(p->force_form != 2 || pl.ok, "vy_talk_attn: the tiled form takes heads <= 32 and vdim <= 128 within 200 KB of shared memory");
+  VY_CHECK_ARG(p->force_form != 2 || pl.ok, "vy_talk_attn: the tiled form takes heads <= 64 and vdim <= 128 within 200 KB of shared memory");
   const bool tiled = p->force_form == 2 || (p->force_form == 0 && pl.ok && p->max_new >= 8);
   if (tiled) {
     cudaError_t e;
-    if (pl.RB == 1) e = pl.MV == 1 ? launch_tiled<1, 1>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st)
-                                   : launch_tiled<1, 2>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st);
-    else e = pl.MV == 1 ? launch_tiled<2, 1>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st)
-                        : launch_tiled<2, 2>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st);
+    if (pl.NT == 512) e = pl.MV == 1 ? launch_tiled<512, 2, 1>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st)
+                                     : launch_tiled<512, 2, 2>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st);
+    else if (pl.RB == 1) e = pl.MV == 1 ? launch_tiled<256, 1, 1>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st)
+                                        : launch_tiled<256, 1, 2>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st);
+    else e = pl.MV == 1 ? launch_tiled<256, 2, 1>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st)
+                        : launch_tiled<256, 2, 2>(d, pl, p->n_seqs, p->max_new, dim4, vdim4, qvec, kvvec, st);
     VY_CUDA_OK(e);
     VY_LAUNCH_OK();
     count_launch();
@@ -537,7 +596,7 @@ extern "C" int vy_talk_attn(const VyTalkAttn* p) {
   VY_LAUNCH_OK();
   count_launch();
   if (splits > 1) {   // single-token steps: row s is sequence s
-    VY_CUDA_OK(launch_kernel(talk_attn_merge_kernel, dim3(static_cast<unsigned>(p->n_seqs)), dim3(128), 0, st, d, p->n_seqs, splits,
+    VY_CUDA_OK(launch_kernel(talk_attn_merge_kernel, dim3(static_cast<unsigned>(p->n_seqs), d.heads), dim3(64), 0, st, d, splits,
                              static_cast<const float*>(p->workspace)));
     VY_LAUNCH_OK();
     count_launch();
