@@ -15,13 +15,16 @@ namespace vy {
 
 constexpr int PB_T = 128;
 
-__device__ __forceinline__ float block_sum_128(float v, float* red) {
+// sum over the CTA (any multiple of 32 threads up to 1024), the same value in every thread
+__device__ __forceinline__ float block_sum(float v, float* red) {
   v = warp_sum(v);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   __syncthreads();   // red may still be read from the previous reduction
   if (lane == 0) red[warp] = v;
   __syncthreads();
-  return red[0] + red[1] + red[2] + red[3];
+  float s = 0.f;
+  for (int w = 0; w < nw; ++w) s += red[w];
+  return s;
 }
 
 struct MixDev {
@@ -39,14 +42,15 @@ struct MixDev {
   void* nout; long long ld_nout; int nout_dt;
 };
 
-// one CTA per row; the row's fp32 values live in shared memory between the passes
+// one CTA per row (128 to 1024 threads, about two columns per thread: the loads of a column cannot pass the stores of the one before,
+// so few columns per thread keep the row's loads in flight together); the row's fp32 values live in shared memory between the passes
 template <bool MIX>
-__global__ void __launch_bounds__(PB_T) depth_mix_norm_kernel(MixDev d) {
+__global__ void __launch_bounds__(1024) depth_mix_norm_kernel(MixDev d) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float pb_row[];   // [width]
-  __shared__ float red[4];
-  const int t = threadIdx.x;
+  __shared__ float red[32];
+  const int t = threadIdx.x, PB_T = blockDim.x;
   for (long long r = blockIdx.x; r < d.rows; r += gridDim.x) {
     __syncthreads();   // the previous row's readers are done with pb_row
     if (MIX) {
@@ -76,13 +80,13 @@ __global__ void __launch_bounds__(PB_T) depth_mix_norm_kernel(MixDev d) {
     float s = 0.f;
     __syncthreads();
     for (int c = t; c < d.width; c += PB_T) s += pb_row[c];
-    const float mean = block_sum_128(s, red) / static_cast<float>(d.width);
+    const float mean = block_sum(s, red) / static_cast<float>(d.width);
     float q = 0.f;
     for (int c = t; c < d.width; c += PB_T) {
       const float u = pb_row[c] - mean;
       q = fmaf(u, u, q);
     }
-    const float inv = 1.f / sqrtf(block_sum_128(q, red) / static_cast<float>(d.width) + d.eps);
+    const float inv = 1.f / sqrtf(block_sum(q, red) / static_cast<float>(d.width) + d.eps);
     for (int c = t; c < d.width; c += PB_T) {
       float v = (pb_row[c] - mean) * inv;
       if (d.nw) v *= ld_as_float(d.nw, d.nw_dt, c);
@@ -195,6 +199,12 @@ __global__ void __launch_bounds__(PB_T) rope_kv_write_kernel(RopeKvDev d) {
     return VY_ERR_NO_DEVICE;                                                   \
   }
 
+static unsigned mix_threads(int width) {
+  unsigned n = 128;
+  while (n < 1024 && static_cast<int>(2 * n) < width) n *= 2;
+  return n;
+}
+
 static cudaError_t mix_smem_ok(size_t smem, bool mix) {
   static size_t allowed[2] = {48 * 1024, 48 * 1024};
   if (smem <= allowed[mix]) return cudaSuccess;
@@ -220,7 +230,7 @@ extern "C" int vy_layer_norm(const VyLayerNorm* p) {
   const size_t smem = sizeof(float) * p->width;
   VY_CUDA_OK(mix_smem_ok(smem, false));
   const unsigned blocks = static_cast<unsigned>(p->tokens < 1048576 ? p->tokens : 1048576);
-  VY_CUDA_OK(launch_kernel(depth_mix_norm_kernel<false>, dim3(blocks), dim3(PB_T), smem, static_cast<cudaStream_t>(p->stream), d));
+  VY_CUDA_OK(launch_kernel(depth_mix_norm_kernel<false>, dim3(blocks), dim3(mix_threads(p->width)), smem, static_cast<cudaStream_t>(p->stream), d));
   VY_LAUNCH_OK();
   count_launch();
   return VY_OK;
@@ -249,7 +259,7 @@ extern "C" int vy_depth_mix(const VyDepthMix* p) {
   const size_t smem = sizeof(float) * p->width;
   VY_CUDA_OK(mix_smem_ok(smem, true));
   const unsigned blocks = static_cast<unsigned>(p->rows < 1048576 ? p->rows : 1048576);
-  VY_CUDA_OK(launch_kernel(depth_mix_norm_kernel<true>, dim3(blocks), dim3(PB_T), smem, static_cast<cudaStream_t>(p->stream), d));
+  VY_CUDA_OK(launch_kernel(depth_mix_norm_kernel<true>, dim3(blocks), dim3(mix_threads(p->width)), smem, static_cast<cudaStream_t>(p->stream), d));
   VY_LAUNCH_OK();
   count_launch();
   return VY_OK;

@@ -54,32 +54,92 @@ __device__ __forceinline__ void load_talk(const TalkDev& d, float* T_s, int H, i
   }
 }
 
+__device__ __forceinline__ int pow2_shift(int n) { return n > 0 && (n & (n - 1)) == 0 ? 31 - __clz(n) : -1; }
+
 __device__ __forceinline__ float gate_of(const TalkDev& d, long long row, int h, int c) {
   if (!d.gate) return 1.f;
   return sigmoidf_(ld_as_float(d.gate, d.gate_dt, row * d.ld_gate + (d.gate_ch ? static_cast<long long>(h) * d.vdim + c : h)));
 }
 
+// Stages the rows krow[j] (j < 2^kn_shift; -1 = zero row) of ALL key/value heads into dst[(g * kn + j) * ld + c] (zero-filled up to
+// width4 columns): pool rows are [G][width]. Index arithmetic by shifts when width4 / 4 is a power of two (w4_shift >= 0); global
+// loads go out in batches of 8 per thread before any of them is used.
+template <int T>
+__device__ __forceinline__ void stage_heads(float* dst, int ld, int G, int kn_shift, int width, int width4, int w4_shift, const void* src, int dt,
+                                            bool vec, const int* krow) {
+  constexpr int U = 8;
+  const int kn = 1 << kn_shift;
+  if (vec) {
+    const int w4 = width4 >> 2, total = (G << kn_shift) * w4;
+    for (int e0 = threadIdx.x; e0 < total; e0 += T * U) {
+      float4 v[U];
+      int at[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int e = e0 + u * T;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        at[u] = -1;
+        if (e < total) {
+          const int jj = w4_shift >= 0 ? e >> w4_shift : e / w4;
+          const int c = (e - jj * w4) << 2, g = jj >> kn_shift, j = jj & (kn - 1);
+          at[u] = jj * ld + c;
+          const int kr = krow[j];
+          if (kr >= 0 && c < width)
+            v[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + (static_cast<long long>(kr) * G + g) * width + c);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (at[u] >= 0) *reinterpret_cast<float4*>(dst + at[u]) = v[u];
+    }
+  } else {
+    const int total = (G << kn_shift) * width4;
+    for (int e0 = threadIdx.x; e0 < total; e0 += T * U) {
+      float v[U];
+      int at[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int e = e0 + u * T;
+        v[u] = 0.f;
+        at[u] = -1;
+        if (e < total) {
+          const int jj = e / width4, c = e - jj * width4, g = jj >> kn_shift, j = jj & (kn - 1);
+          at[u] = jj * ld + c;
+          const int kr = krow[j];
+          if (kr >= 0 && c < width) v[u] = ld_as_float(src, dt, (static_cast<long long>(kr) * G + g) * width + c);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (at[u] >= 0) dst[at[u]] = v[u];
+    }
+  }
+}
+
 // ---- rows form ------------------------------------------------------------------------------------------------------------------
 constexpr int TR_T = 256;   // threads
-constexpr int TR_N = 64;    // keys per tile
 
-// grid (token of the sequence, sequence, split). Shared memory (floats): q [H][dim4] | staged rows [TR_N][ld_s] | S [H][TR_N] |
-// P [H][TR_N] | talk transposed [H][Hp] (Hp = H rounded up to 4, zero padded) | m, l, corr [H] each | acc [H][vdim] | key rows (int) [TR_N].
-__global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim4, int vdim4, int ld_s, bool qvec, bool kvvec, int splits, float* ws) {
+// grid (token of the sequence, sequence, split); kn keys per tile (64, 32 or 16, by the shared memory they take). Shared memory
+// (floats): q [H][dim4] | staged rows [G][kn][ld_s] (keys, then values, of ALL key/value heads) | S [H][kn] | P [H][kn] |
+// talk transposed [H][Hp] (Hp = H rounded up to 4, zero padded) | m, l, corr [H] each | acc [H][vdim4] | key rows (int) [kn].
+// HB: query heads per thread in the score phase (they share the staged key row): 4 or 2 when the heads per key/value head allow.
+template <int HB>
+__global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int kn, int dim4, int vdim4, int ld_s, bool qvec, bool kvvec, int splits, float* ws) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) float tr_smem[];
   const int H = d.heads, G = d.kv_heads, per = H / G, Hp = (H + 3) & ~3;
+  const int kn_shift = 31 - __clz(kn), dsh = pow2_shift(dim4 >> 2), vsh = pow2_shift(vdim4 >> 2);
   float* q_s = tr_smem;
   float* kv_s = q_s + H * dim4;
-  float* S_s = kv_s + TR_N * ld_s;
-  float* P_s = S_s + H * TR_N;
-  float* T_s = P_s + H * TR_N;          // T_s[b * Hp + h] = talk[h, b]
-  float* m_s = T_s + H * Hp;
+  float* S_s = kv_s + G * kn * ld_s;
+  float* P_s = S_s + H * kn;
+  float* T_s = P_s + H * kn;            // T_s[b * Hp + h] = talk[h, b]
+  float* acc_s = T_s + H * Hp;          // [H][vdim4]
+  float* m_s = acc_s + H * vdim4;
   float* l_s = m_s + H;
   float* c_s = l_s + H;
-  float* acc_s = c_s + H;
-  int* krow_s = reinterpret_cast<int*>(acc_s + H * d.vdim);
+  int* krow_s = reinterpret_cast<int*>(c_s + H);
   const int s = blockIdx.y, i = blockIdx.x, split = blockIdx.z;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int base = d.cu[s], n = d.cu[s + 1] - base;
@@ -88,7 +148,7 @@ __global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim
   const int p = d.pos0[s] + i;
   const int lo = d.window > 0 ? max(p - d.window + 1, 0) : 0;
   const int count = p - lo + 1;
-  const int tiles = (count + TR_N - 1) / TR_N;
+  const int tiles = (count + kn - 1) / kn;
   const int tps = (tiles + splits - 1) / splits;
   const int tile0 = split * tps, tile1 = min(tiles, tile0 + tps);
   const int* tab = d.table + static_cast<long long>(s) * d.tw;
@@ -103,56 +163,63 @@ __global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim
     m_s[h] = has ? sk : -INFINITY;
     l_s[h] = has ? 1.f : 0.f;
   }
-  for (int e = t; e < H * d.vdim; e += TR_T) acc_s[e] = 0.f;
+  for (int e = t; e < H * vdim4; e += TR_T) acc_s[e] = 0.f;
 
   for (int tile = tile0; tile < tile1; ++tile) {
-    const int c0 = tile * TR_N;
-    const int nk = min(TR_N, count - c0);
+    const int c0 = tile * kn;
+    const int nk = min(kn, count - c0);
     __syncthreads();
-    if (t < TR_N) {
+    if (t < kn) {
       const int kp = lo + c0 + t;
       krow_s[t] = t < nk ? tab[kp / d.bs] * d.bs + kp % d.bs : -1;
     }
-    for (int g = 0; g < G; ++g) {
-      __syncthreads();
-      rows_to_smem<TR_T>(kv_s, ld_s, TR_N, d.dim, dim4, d.kp, d.pool_dt, kvvec, VY_UACT_NONE,
-                         [&](int j) { return krow_s[j] >= 0 ? (static_cast<long long>(krow_s[j]) * G + g) * d.dim : -1LL; });
-      __syncthreads();
-      for (int it = t; it < per * TR_N; it += TR_T) {
-        const int hh = it / TR_N, j = it - hh * TR_N, h = g * per + hh;
-        const float* qp = q_s + h * dim4;
-        const float* kp = kv_s + j * ld_s;
-        float a = 0.f;
-        for (int c = 0; c < dim4; c += 4) a = dot4(f4(qp + c), f4(kp + c), a);
-        S_s[h * TR_N + j] = cap_score(a * d.scale, d.softcap, two_over_cap);
+    __syncthreads();
+    stage_heads<TR_T>(kv_s, ld_s, G, kn_shift, d.dim, dim4, dsh, d.kp, d.pool_dt, kvvec, krow_s);
+    __syncthreads();
+    // raw scores: HB heads of one key/value head against one staged key row per thread
+    for (int it = t; it < (H / HB) * kn; it += TR_T) {
+      const int hb = it >> kn_shift, j = it & (kn - 1), h0 = hb * HB;
+      const float* kp = kv_s + ((h0 / per) * kn + j) * ld_s;
+      const float* qp = q_s + h0 * dim4;
+      float a[HB];
+#pragma unroll
+      for (int u = 0; u < HB; ++u) a[u] = 0.f;
+      for (int c = 0; c < dim4; c += 4) {
+        const float4 k4 = f4(kp + c);
+#pragma unroll
+        for (int u = 0; u < HB; ++u) a[u] = dot4(f4(qp + u * dim4 + c), k4, a[u]);
       }
+#pragma unroll
+      for (int u = 0; u < HB; ++u) S_s[(h0 + u) * kn + j] = cap_score(a[u] * d.scale, d.softcap, two_over_cap);
     }
     __syncthreads();
-    for (int it = t; it < (Hp >> 2) * TR_N; it += TR_T) {   // 4 receiving heads of one key per thread
-      const int hq = it / TR_N, j = it - hq * TR_N;
+    // the value rows replace the keys while the exchange and the softmax run from S_s / P_s
+    stage_heads<TR_T>(kv_s, ld_s, G, kn_shift, d.vdim, vdim4, vsh, d.vp, d.pool_dt, kvvec, krow_s);
+    for (int it = t; it < (Hp >> 2) * kn; it += TR_T) {   // exchange: 4 receiving heads of one key per thread
+      const int hq = it >> kn_shift, j = it & (kn - 1);
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int b = 0; b < H; ++b) {
         const float4 w = f4(T_s + b * Hp + 4 * hq);
-        const float x = S_s[b * TR_N + j];
+        const float x = S_s[b * kn + j];
         a.x = fmaf(w.x, x, a.x); a.y = fmaf(w.y, x, a.y); a.z = fmaf(w.z, x, a.z); a.w = fmaf(w.w, x, a.w);
       }
       const bool live = j < nk;
       const int h0 = 4 * hq;
-      P_s[h0 * TR_N + j] = live ? a.x : -INFINITY;
-      if (h0 + 1 < H) P_s[(h0 + 1) * TR_N + j] = live ? a.y : -INFINITY;
-      if (h0 + 2 < H) P_s[(h0 + 2) * TR_N + j] = live ? a.z : -INFINITY;
-      if (h0 + 3 < H) P_s[(h0 + 3) * TR_N + j] = live ? a.w : -INFINITY;
+      P_s[h0 * kn + j] = live ? a.x : -INFINITY;
+      if (h0 + 1 < H) P_s[(h0 + 1) * kn + j] = live ? a.y : -INFINITY;
+      if (h0 + 2 < H) P_s[(h0 + 2) * kn + j] = live ? a.z : -INFINITY;
+      if (h0 + 3 < H) P_s[(h0 + 3) * kn + j] = live ? a.w : -INFINITY;
     }
     __syncthreads();
     for (int h = warp; h < H; h += TR_T / 32) {
-      float* pr = P_s + h * TR_N;
-      const float a = pr[lane], b = pr[lane + 32];
+      float* pr = P_s + h * kn;
+      const float a = lane < kn ? pr[lane] : -INFINITY, b = lane + 32 < kn ? pr[lane + 32] : -INFINITY;
       const float mo = m_s[h];
       const float mn = fmaxf(mo, warp_max(fmaxf(a, b)));
       const float cr = mn == -INFINITY ? 1.f : expf(mo - mn);
       const float pa = a == -INFINITY ? 0.f : expf(a - mn), pb = b == -INFINITY ? 0.f : expf(b - mn);
-      pr[lane] = pa;
-      pr[lane + 32] = pb;
+      if (lane < kn) pr[lane] = pa;
+      if (lane + 32 < kn) pr[lane + 32] = pb;
       const float sum = warp_sum(pa + pb);
       if (lane == 0) {
         l_s[h] = fmaf(l_s[h], cr, sum);
@@ -160,18 +227,24 @@ __global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim
         c_s[h] = cr;
       }
     }
-    for (int g = 0; g < G; ++g) {
-      __syncthreads();
-      rows_to_smem<TR_T>(kv_s, ld_s, TR_N, d.vdim, vdim4, d.vp, d.pool_dt, kvvec, VY_UACT_NONE,
-                         [&](int j) { return krow_s[j] >= 0 ? (static_cast<long long>(krow_s[j]) * G + g) * d.vdim : -1LL; });
-      __syncthreads();
-      for (int o = t; o < per * d.vdim; o += TR_T) {
-        const int hh = o / d.vdim, c = o - hh * d.vdim, h = g * per + hh;
-        const float* pr = P_s + h * TR_N;
-        float a = acc_s[h * d.vdim + c] * c_s[h];
-        for (int j = 0; j < nk; ++j) a = fmaf(pr[j], kv_s[j * ld_s + c], a);
-        acc_s[h * d.vdim + c] = a;
+    __syncthreads();
+    // values: 4 adjacent channels of one head per thread, 4 keys per step (weights past the last key are 0, their rows zero-filled)
+    const int nk4 = (nk + 3) & ~3, vq = vdim4 >> 2;
+    for (int o = t; o < H * vq; o += TR_T) {
+      const int h = o / vq, c4 = (o - h * vq) << 2;
+      const float* pr = P_s + h * kn;
+      const float* vp = kv_s + (h / per) * kn * ld_s + c4;
+      float* ap = acc_s + h * vdim4 + c4;
+      const float cr = c_s[h];
+      float a[4] = {ap[0] * cr, ap[1] * cr, ap[2] * cr, ap[3] * cr};
+      for (int j4 = 0; j4 < nk4; j4 += 4) {
+        const float4 p4 = f4(pr + j4);
+        axpy4(a, p4.x, f4(vp + (j4 + 0) * ld_s));
+        axpy4(a, p4.y, f4(vp + (j4 + 1) * ld_s));
+        axpy4(a, p4.z, f4(vp + (j4 + 2) * ld_s));
+        axpy4(a, p4.w, f4(vp + (j4 + 3) * ld_s));
       }
+      *reinterpret_cast<float4*>(ap) = make_float4(a[0], a[1], a[2], a[3]);
     }
   }
   __syncthreads();
@@ -179,7 +252,7 @@ __global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim
     for (int o = t; o < H * d.vdim; o += TR_T) {
       const int h = o / d.vdim, c = o - h * d.vdim;
       const float l = l_s[h];
-      st_from_float(d.out, d.out_dt, qrow * d.ld_out + o, l > 0.f ? acc_s[o] / l * gate_of(d, qrow, h, c) : 0.f);
+      st_from_float(d.out, d.out_dt, qrow * d.ld_out + o, l > 0.f ? acc_s[h * vdim4 + c] / l * gate_of(d, qrow, h, c) : 0.f);
     }
   } else {
     // part of (row, split): [H] max | [H] sum | [H * vdim] unnormalised output
@@ -188,7 +261,7 @@ __global__ void __launch_bounds__(TR_T) talk_attn_rows_kernel(TalkDev d, int dim
       w[h] = m_s[h];
       w[H + h] = l_s[h];
     }
-    for (int o = t; o < H * d.vdim; o += TR_T) w[2 * H + o] = acc_s[o];
+    for (int o = t; o < H * d.vdim; o += TR_T) w[2 * H + o] = acc_s[(o / d.vdim) * vdim4 + o % d.vdim];
   }
 }
 
@@ -260,6 +333,7 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
   const int count = p_hi - lo + 1;
   const int* tab = d.table + static_cast<long long>(s) * d.tw;
   const float two_over_cap = d.softcap > 0.f ? 2.f / d.softcap : 0.f;
+  const int dsh = pow2_shift(dim4 >> 2), vsh = pow2_shift(vdim4 >> 2);
   for (int r = t; r < R; r += TT_T) {
     float sk;
     const bool has = r < rows && sink_of(d, r / TQ, sk);
@@ -288,10 +362,7 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
       krow_s[t] = t < nk ? tab[kp / d.bs] * d.bs + kp % d.bs : -1;
     }
     __syncthreads();
-    rows_to_smem<TT_T>(K_s, ldkv, G * KN, d.dim, dim4, d.kp, d.pool_dt, kvvec, VY_UACT_NONE, [&](int jj) {
-      const int g = jj / KN, j = jj - g * KN;
-      return krow_s[j] >= 0 ? (static_cast<long long>(krow_s[j]) * G + g) * d.dim : -1LL;
-    });
+    stage_heads<TT_T>(K_s, ldkv, G, KN == 32 ? 5 : 4, d.dim, dim4, dsh, d.kp, d.pool_dt, kvvec, krow_s);
     __syncthreads();
     // raw scores
 #pragma unroll
@@ -323,10 +394,7 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
     }
     __syncthreads();
     // values replace the keys while the exchange and the softmax run from S_s / P_s
-    rows_to_smem<TT_T>(K_s, ldkv, G * KN, d.vdim, vdim4, d.vp, d.pool_dt, kvvec, VY_UACT_NONE, [&](int jj) {
-      const int g = jj / KN, j = jj - g * KN;
-      return krow_s[j] >= 0 ? (static_cast<long long>(krow_s[j]) * G + g) * d.vdim : -1LL;
-    });
+    stage_heads<TT_T>(K_s, ldkv, G, KN == 32 ? 5 : 4, d.vdim, vdim4, vsh, d.vp, d.pool_dt, kvvec, krow_s);
     // exchange + mask: element (h, i, j) of P = sum_b talk[h, b] S[b, i, j]
     // each thread: 4 receiving heads x one query x 4 keys, reading every head's raw scores of that (query, keys) once
     for (int it = t; it < (Hp >> 2) * TQ * (KN / 4); it += TT_T) {
@@ -455,6 +523,8 @@ talk_attn_tiled_kernel(TalkDev d, int TQ, int dim4, int vdim4, int ldq_s, int ld
 }
 
 // ---- host side ----------------------------------------------------------------------------------------------------------------
+constexpr int TR_N = 64;   // most keys per tile of the rows form; the split count is planned with it
+
 static int rows_splits(int n_seqs, int max_new, int table_width, int block_size) {
   // single-token steps only: enough CTAs for four per SM (the latency of a tile's loads is hidden by other CTAs), at most one per key tile, at most 64
   if (max_new != 1) return 1;
@@ -466,9 +536,9 @@ static int rows_splits(int n_seqs, int max_new, int table_width, int block_size)
   return want < 1 ? 1 : static_cast<int>(want);
 }
 
-static size_t rows_smem(const TalkDev& d, int dim4, int ld_s) {
+static size_t rows_smem(const TalkDev& d, int kn, int dim4, int vdim4, int ld_s) {
   const size_t H = d.heads;
-  return sizeof(float) * (H * dim4 + static_cast<size_t>(TR_N) * ld_s + 2 * H * TR_N + H * ((H + 3) & ~3) + 3 * H + H * d.vdim) + sizeof(int) * TR_N;
+  return sizeof(float) * (H * dim4 + static_cast<size_t>(d.kv_heads) * kn * ld_s + 2 * H * kn + H * ((H + 3) & ~3) + 3 * H + H * vdim4) + sizeof(int) * kn;
 }
 
 static int pad_ld(int w4) { return ((w4 >> 2) & 1) ? w4 + 8 : w4 + 4; }   // (row stride / 4) odd: rows 1 apart start in distinct 16-byte bank groups
@@ -577,13 +647,23 @@ extern "C" int vy_talk_attn(const VyTalkAttn* p) {
     return VY_OK;
   }
   const int ld_s = pad_ld(dim4 > vdim4 ? dim4 : vdim4);
-  const size_t smem = rows_smem(d, dim4, ld_s);
+  // keys per tile: 64 when two CTAs still share an SM, else the most that fit
+  int kn = TR_N;
+  while (kn > 16 && rows_smem(d, kn, dim4, vdim4, ld_s) > 110 * 1024) kn >>= 1;
+  if (rows_smem(d, kn, dim4, vdim4, ld_s) > 110 * 1024) {
+    kn = TR_N;
+    while (kn > 16 && rows_smem(d, kn, dim4, vdim4, ld_s) > 220 * 1024) kn >>= 1;
+  }
+  const size_t smem = rows_smem(d, kn, dim4, vdim4, ld_s);
   VY_CHECK_ARG(smem <= 220 * 1024, "vy_talk_attn: %d heads of %d / %d channels need %zu bytes of shared memory per CTA (at most 220 KB)", d.heads, d.dim,
                d.vdim, smem);
-  static size_t allowed = 48 * 1024;
-  if (smem > allowed) {
-    VY_CUDA_OK(cudaFuncSetAttribute(talk_attn_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    allowed = smem;
+  const int per = d.heads / d.kv_heads;
+  const int hb = per % 4 == 0 ? 4 : per % 2 == 0 ? 2 : 1;
+  auto kern = hb == 4 ? talk_attn_rows_kernel<4> : hb == 2 ? talk_attn_rows_kernel<2> : talk_attn_rows_kernel<1>;
+  static size_t allowed[3] = {48 * 1024, 48 * 1024, 48 * 1024};
+  if (smem > allowed[hb >> 1]) {
+    VY_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    allowed[hb >> 1] = smem;
   }
   int splits = rows_splits(p->n_seqs, p->max_new, p->table_width, p->block_size);
   const long long rows_bound = static_cast<long long>(p->n_seqs) * p->max_new;
@@ -591,7 +671,7 @@ extern "C" int vy_talk_attn(const VyTalkAttn* p) {
     const long long need = rows_bound * splits * d.heads * (d.vdim + 2);
     if (!p->workspace || p->workspace_floats < need) splits = 1;   // no scratch given: every query walks all its keys in one CTA
   }
-  VY_CUDA_OK(launch_kernel(talk_attn_rows_kernel, dim3(p->max_new, p->n_seqs, splits), dim3(TR_T), smem, st, d, dim4, vdim4, ld_s, qvec, kvvec, splits,
+  VY_CUDA_OK(launch_kernel(kern, dim3(p->max_new, p->n_seqs, splits), dim3(TR_T), smem, st, d, kn, dim4, vdim4, ld_s, qvec, kvvec, splits,
                            p->workspace));
   VY_LAUNCH_OK();
   count_launch();
