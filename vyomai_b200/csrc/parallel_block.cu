@@ -113,12 +113,38 @@ __device__ __forceinline__ float clamped_glu(float g, float u, float limit, floa
   return g * sigmoidf_(alpha * g) * (u + 1.f);
 }
 
-// blockIdx.x = token, threads (and blockIdx.y) over output columns
+// blockIdx.x = token, threads (and blockIdx.y) over output columns. VEC: 8 adjacent columns per thread with 16 / 32-byte accesses
+// (ff and shared_ff multiples of 8, aligned rows); an unchosen expert's columns are written 0 without reading its hidden values.
+template <bool VEC>
 __global__ void __launch_bounds__(256) moe_glu_kernel(GluDev d) {
   pdl_trigger();
   pdl_wait();
   const long long r = blockIdx.x;
   const int ecols = d.experts * d.ff, cols = ecols + d.shared_ff;
+  if (VEC) {
+    for (int c0 = (blockIdx.y * 256 + threadIdx.x) * 8; c0 < cols; c0 += gridDim.y * 256 * 8) {
+      float y[8];
+      const bool routed = c0 < ecols;
+      const int e = routed ? c0 / d.ff : d.experts;
+      const int j = routed ? c0 - e * d.ff : c0 - ecols;
+      const int half = routed ? d.ff : d.shared_ff;
+      const float w = routed ? (d.dense ? d.dense[r * d.ld_dense + e] : 1.f) : 1.f;
+      if (w != 0.f) {
+        const long long o = r * d.ldh + static_cast<long long>(e) * 2 * d.ff + j;   // the shared block follows the experts' 2 ff columns each
+        float g[8], u[8];
+        ld8_as_float(d.h, d.h_dt, o, g);
+        ld8_as_float(d.h, d.h_dt, o + half, u);
+        const float lim = routed ? d.limit : d.shared_limit;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) y[k] = w * clamped_glu(g[k], u[k], lim, d.alpha);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) y[k] = 0.f;
+      }
+      st8_from_float(d.out, d.out_dt, r * d.ld_out + c0, y);
+    }
+    return;
+  }
   for (int c = blockIdx.y * 256 + threadIdx.x; c < cols; c += gridDim.y * 256) {
     float y = 0.f;
     if (c < ecols) {
@@ -279,9 +305,15 @@ extern "C" int vy_moe_glu(const VyMoeGlu* p) {
   d.limit = p->limit; d.shared_limit = p->shared_limit; d.alpha = p->alpha;
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
   const int cols = d.experts * d.ff + d.shared_ff;
-  int gy = (cols + 255) / 256;
+  const auto al = [](const void* q, size_t n) { return reinterpret_cast<uintptr_t>(q) % n == 0; };
+  const size_t hb = p->h_dtype == VY_F32 ? 32 : 16, ob = p->out_dtype == VY_F32 ? 32 : 16;
+  const bool vec = (d.experts == 0 || d.ff % 8 == 0) && d.shared_ff % 8 == 0 && p->ldh % 8 == 0 && p->ld_out % 8 == 0 && al(p->h, hb) && al(p->out, ob);
+  const int per_cta = vec ? 2048 : 256;
+  int gy = (cols + per_cta - 1) / per_cta;
   if (gy > 64) gy = 64;
-  VY_CUDA_OK(launch_kernel(moe_glu_kernel, dim3(static_cast<unsigned>(p->rows), gy), dim3(256), 0, static_cast<cudaStream_t>(p->stream), d));
+  const dim3 grid(static_cast<unsigned>(p->rows), gy);
+  VY_CUDA_OK(vec ? launch_kernel(moe_glu_kernel<true>, grid, dim3(256), 0, static_cast<cudaStream_t>(p->stream), d)
+                 : launch_kernel(moe_glu_kernel<false>, grid, dim3(256), 0, static_cast<cudaStream_t>(p->stream), d));
   VY_LAUNCH_OK();
   count_launch();
   return VY_OK;
