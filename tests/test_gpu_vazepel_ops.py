@@ -161,7 +161,7 @@ def test_rotation_and_page_write(rot_dims):
     assert torch.equal(Pd[:, -5:].cpu(), P[:, -5:]) and int((kp == 7.0).sum()) == kp.numel() - rows * G * d
 
 
-def _attn_oracle(q, k, v, talk, m, gate):
+def _attn_oracle(q, k, v, talk, m, gate, window=0):
     """q [T, H, d], k [T, G, d], v [T, G, dv] already rotated -> [T, H * dv] after the gate."""
     T, H, G = q.shape[0], m["heads"], m["kv_heads"]
     per = H // G
@@ -170,12 +170,13 @@ def _attn_oracle(q, k, v, talk, m, gate):
         s = O.capped(s, m["softcap"])
     if talk is not None:
         s = O.mix_heads(s, talk)
-    p = O.plus_one_softmax(s, torch.arange(T)[:, None] >= torch.arange(T)[None, :])
+    back = torch.arange(T)[:, None] - torch.arange(T)[None, :]
+    p = O.plus_one_softmax(s, (back >= 0) & (back < window) if window else back >= 0)
     o = torch.stack([p[a] @ v[:, a // per] for a in range(H)], 1).reshape(T, -1)
     return o * torch.sigmoid(gate)
 
 
-def _run_attn(m, q, k, v, talk, gate, steps, form, bs=4):
+def _run_attn(m, q, k, v, talk, gate, steps, form, bs=4, window=0):
     """Feeds one sequence in portions through real (shuffled) pages with the chosen form of the kernel."""
     from vyomai_b200 import ops
     T, H, G, d, dv = q.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -188,7 +189,7 @@ def _run_attn(m, q, k, v, talk, gate, steps, form, bs=4):
         batch = ops.PackedBatch(t([0, n]), t([at]), t([0]), n, t(order).view(1, -1), bs)
         ops.kv_page_write(batch, k[at:at + n].reshape(n, -1).float().to(DEV), v[at:at + n].reshape(n, -1).float().to(DEV), kp, vp)
         outs.append(ops.talk_attn(batch, q[at:at + n].reshape(n, -1).float().to(DEV), kp, vp, heads=H, kv_heads=G, dim=d, vdim=dv, scale=m["scale"],
-                                  softcap=m["softcap"], talk=None if talk is None else talk.float().to(DEV), zero_sink=True,
+                                  softcap=m["softcap"], talk=None if talk is None else talk.float().to(DEV), zero_sink=True, window=window,
                                   gate=gate[at:at + n].float().to(DEV), gate_per_channel=True, form=form).cpu())
         at += n
     return torch.cat(outs)
@@ -248,6 +249,30 @@ def test_the_extra_unit_in_the_denominator(form):
     q[:, :, 0], k[:, :, 0] = 10.0, -10.0
     got = _run_attn(m, q, k, v, None, gate, [T], form)
     assert float(got.abs().max()) < 1e-30 or float(got.abs().max()) < 1e-20
+
+
+@pytest.mark.parametrize("form", ["rows", "tiled"])
+@pytest.mark.parametrize("window,steps", [(5, [60]), (16, [40, 1, 1, 18]), (33, [2] * 30), (64, [59, 1])])
+def test_window_option_just_inside_and_just_outside(form, window, steps):
+    """The kernel's optional sliding window (0 in Vazepel itself): against the oracle, and the key exactly `window` back does not reach
+    the last query while the key `window - 1` back does; in prompts, portions and single tokens, with the edge at and off page and tile
+    borders."""
+    m = U.attn(heads=4, kv_heads=2, dim=8, vdim=5, scale=0.5, softcap=6.0)
+    g = _g(window)
+    T = 60
+    q, k, v = torch.randn(T, 4, 8, generator=g), torch.randn(T, 2, 8, generator=g), torch.randn(T, 2, 5, generator=g)
+    talk = torch.eye(4) + torch.randn(4, 4, generator=g) * 0.3
+    gate = torch.randn(T, 20, generator=g)
+    want = _attn_oracle(q.double(), k.double(), v.double(), talk.double(), m, gate.double(), window=window)
+    got = _run_attn(m, q, k, v, talk, gate, steps, form, window=window)
+    assert HU.rel_err(got, want) < 2e-5
+    if window < T:
+        for back, same in ((window, True), (window - 1, False)):
+            k2, v2 = k.clone(), v.clone()
+            k2[T - 1 - back] += 3.0
+            v2[T - 1 - back] += 3.0
+            other = _run_attn(m, q, k2, v2, talk, gate, steps, form, window=window)[-1]
+            assert torch.equal(other, got[-1]) == same, (back, same)
 
 
 def test_single_tokens_split_their_keys_over_ctas():

@@ -648,7 +648,8 @@ extern "C" int vy_talk_attn(const VyTalkAttn* p) {
   }
   const int ld_s = pad_ld(dim4 > vdim4 ? dim4 : vdim4);
   // keys per tile: 64 when two CTAs still share an SM, else the most that fit
-  int kn = TR_N;
+  static const int kn_env = getenv("VY_TALK_ATTN_KN") ? atoi(getenv("VY_TALK_ATTN_KN")) : 0;   // development: 64, 32 or 16
+  int kn = kn_env == 32 || kn_env == 16 ? kn_env : TR_N;
   while (kn > 16 && rows_smem(d, kn, dim4, vdim4, ld_s) > 110 * 1024) kn >>= 1;
   if (rows_smem(d, kn, dim4, vdim4, ld_s) > 110 * 1024) {
     kn = TR_N;
