@@ -198,9 +198,12 @@ def _run_attn(m, q, k, v, talk, gate, steps, form, bs=4, window=0):
 @pytest.mark.parametrize("form", ["rows", "tiled"])
 @pytest.mark.parametrize("shape", [dict(heads=6, kv_heads=3, dim=10, vdim=7), dict(heads=8, kv_heads=2, dim=32, vdim=24), dict(heads=3, kv_heads=1, dim=6, vdim=70),
                                    dict(heads=24, kv_heads=4, dim=12, vdim=72), dict(heads=5, kv_heads=5, dim=4, vdim=3), dict(heads=40, kv_heads=8, dim=8, vdim=6),
-                                   dict(heads=16, kv_heads=4, dim=64, vdim=64)])
+                                   dict(heads=16, kv_heads=4, dim=64, vdim=64), dict(heads=48, kv_heads=48, dim=64, vdim=8)])
 @pytest.mark.parametrize("steps", [[75], [40, 1, 1, 33], [2] * 37 + [1]])
 def test_score_exchanging_attention(form, shape, steps):
+    """The last shape's key rows of all 48 key/value heads do not fit a 16-key tile: the tiled form refuses it (the automatic choice
+    never takes it there) and the one-query form drops to 8 keys per tile."""
+    from vyomai_b200._lib import VyomError
     m = U.attn(scale=0.4, softcap=3.0, **shape)
     g = _g(shape["heads"])
     T, H, G, d, dv = 75, m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -208,6 +211,10 @@ def test_score_exchanging_attention(form, shape, steps):
     talk = torch.eye(H) + torch.randn(H, H, generator=g) * 0.5
     gate = torch.randn(T, H * dv, generator=g)
     want = _attn_oracle(q.double(), k.double(), v.double(), talk.double(), m, gate.double())
+    if form == "tiled" and H == 48:
+        with pytest.raises(VyomError):
+            _run_attn(m, q, k, v, talk, gate, steps, form)
+        form = None
     got = _run_attn(m, q, k, v, talk, gate, steps, form)
     assert HU.rel_err(got, want) < 2e-5
 

@@ -119,7 +119,7 @@ __device__ __forceinline__ void stage_heads(float* dst, int ld, int G, int kn_sh
 // ---- rows form ------------------------------------------------------------------------------------------------------------------
 constexpr int TR_T = 256;   // threads
 
-// grid (token of the sequence, sequence, split); kn keys per tile (64, 32 or 16, by the shared memory they take). Shared memory
+// grid (token of the sequence, sequence, split); kn keys per tile (a power of two from 64 down to 4, by the shared memory they take). Shared memory
 // (floats): q [H][dim4] | staged rows [G][kn][ld_s] (keys, then values, of ALL key/value heads) | S [H][kn] | P [H][kn] |
 // talk transposed [H][Hp] (Hp = H rounded up to 4, zero padded) | m, l, corr [H] each | acc [H][vdim4] | key rows (int) [kn].
 // HB: query heads per thread in the score phase (they share the staged key row): 4 or 2 when the heads per key/value head allow.
@@ -653,7 +653,7 @@ extern "C" int vy_talk_attn(const VyTalkAttn* p) {
   while (kn > 16 && rows_smem(d, kn, dim4, vdim4, ld_s) > 110 * 1024) kn >>= 1;
   if (rows_smem(d, kn, dim4, vdim4, ld_s) > 110 * 1024) {
     kn = TR_N;
-    while (kn > 16 && rows_smem(d, kn, dim4, vdim4, ld_s) > 220 * 1024) kn >>= 1;
+    while (kn > 4 && rows_smem(d, kn, dim4, vdim4, ld_s) > 220 * 1024) kn >>= 1;   // many wide key/value heads: few keys per tile, still exact
   }
   const size_t smem = rows_smem(d, kn, dim4, vdim4, ld_s);
   VY_CHECK_ARG(smem <= 220 * 1024, "vy_talk_attn: %d heads of %d / %d channels need %zu bytes of shared memory per CTA (at most 220 KB)", d.heads, d.dim,
