@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define VY_ABI_VERSION 10
+#define VY_ABI_VERSION 11
 
 #if defined(__GNUC__)
 #define VY_API __attribute__((visibility("default")))
@@ -652,10 +652,11 @@ VY_API int vy_linear_plain(const VyLinear* p);
 /* Grouped RMS norm with optional weight, gate, row gather and accumulation. Row r = (token r / groups, group r % groups),
  * source token st = row_index ? row_index[token] : token:
  *   xn[c]  = x[st * ldx + group * width + c] / sqrt(mean_c(x^2) + eps)
- *   y[c]   = coef * xn[c] * (w_mode == 0 ? 1 : w_mode == 1 ? weight[c] : 1 + weight[c])
- *                 * (gate ? (gate_act == VY_UACT_SIGMOID ? sigmoid(gate[st * ld_gate + group * width + c]) : gate[..]) : 1)
+ *   y[c]   = coef * xn[c] * (w_mode == 0 ? 1 : w_mode == 1 ? weight[wc] : 1 + weight[wc])
+ *                 * (gate ? gate_act(gate[st * ld_gate + group * width + c]) : 1)       (gate_act: any VY_UACT_*, NONE = the gate itself)
  *   out[token * ld_out + group * width + c] = (accumulate ? out[..] : 0) + y[c]
- * weight is [width], shared by the groups. coef 0 = 1. */
+ * weight is [width], shared by the groups (wc = c), or with w_full [groups * width], one entry per element of the row
+ * (wc = group * width + c). coef 0 = 1. */
 typedef struct VyRmsNorm {
   int64_t tokens;
   int32_t groups, width;
@@ -670,8 +671,21 @@ typedef struct VyRmsNorm {
    * input of the next product beside an fp32 residual that was just accumulated into) */
   void* copy; int64_t ld_copy; int32_t copy_dtype;
   void* stream;
+  int32_t w_full;
 } VyRmsNorm;
 VY_API int vy_rms_norm(const VyRmsNorm* p);
+
+/* Polynomial activation with normalised powers, row by row in fp32: with N(u) = u / sqrt(mean_c(u^2) + eps) over the row,
+ *   out[r, c] = a N(z)[c] + b N(z^2)[c] + c3 N(z^3)[c] + e,   z = x[r, :], powers element by element.
+ * width <= 49152 (the row is held in shared memory). */
+typedef struct VyPolyNorm {
+  int64_t rows; int32_t width;
+  const void* x; int64_t ldx; int32_t x_dtype;
+  float a, b, c3, e, eps;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  void* stream;
+} VyPolyNorm;
+VY_API int vy_poly_norm(const VyPolyNorm* p);
 
 /* out[r, c] = act(x[r, c]) with a dtype change (the activation between two tensor-core GEMMs, computed in fp32). */
 VY_API int vy_unary(int64_t rows, int32_t cols, const void* x, int64_t ldx, int32_t x_dtype, int32_t act, void* out, int64_t ld_out,
@@ -695,7 +709,9 @@ typedef struct VyKvWrite {
 VY_API int vy_kv_page_write(const VyKvWrite* p);
 
 /* Windowed attention over the paged pools. The query at position i of sequence s sees key j iff
- * j <= i and (i - j < window or j < keep_first); window <= 0 = no window (plain causal). Kept keys enter with their own
+ * j <= i and (i - j < window or j < keep_first); window <= 0 = no window (plain causal). With chunk > 0 (instead of a window:
+ * window and keep_first must be 0) it sees key j iff j <= i and i / chunk == j / chunk (integer division): positions form
+ * consecutive blocks of `chunk`, counted from position 0 of the sequence, and attention stays inside a block. Kept keys enter with their own
  * rows of the cache; positions do not enter the score otherwise. score = (q . k) * scale. With `sink` (one number per
  * query head) the softmax denominator also holds exp(sink[h]): it has no key and no value. With `gate` the head's
  * output is multiplied by sigmoid(gate[token, h]). Query head h reads kv head h / (heads / kv_heads). The step's own
@@ -721,6 +737,8 @@ typedef struct VyWinAttn {
    * key / value rows in groups of 8 or more split a sequence's keys over several CTAs and combine the parts from here */
   float* workspace; int64_t workspace_floats;
   void* stream;
+  int32_t chunk;
+  float out_scale; /* multiplies the output (0 = 1): a mixer's weight in a sum of mixers, applied in fp32 before the output is rounded */
 } VyWinAttn;
 VY_API int64_t vy_window_attn_workspace_floats(int32_t n_seqs, int32_t heads, int32_t kv_heads, int32_t vdim);
 VY_API int vy_window_attn(const VyWinAttn* p);
@@ -783,10 +801,29 @@ typedef struct VyDeltaRule {
 VY_API int64_t vy_delta_rule_workspace_floats(int64_t rows, int32_t heads, int32_t kv_heads, int32_t dim);
 VY_API int vy_delta_rule(const VyDeltaRule* p);
 
+/* Gated linear attention, state carried per sequence: a decay per key channel and token, no correction term. Per head h and token t:
+ *   g[i] = sigmoid(a[t, h * dim + i])^(1 / tau) = exp(-softplus(-a) / tau)                       (fp32)
+ *   S <- diag(g) S + k_t v_t^T;   o_t = S^T (q_t * q_scale)                                        (S is dim x vdim, fp32)
+ * state is [slots, heads, dim, vdim] fp32; dim <= 256. workspace: rows * heads * dim floats (the decays of all tokens, computed by
+ * one parallel launch before the token-serial kernel). q_scale 0 = 1. */
+typedef struct VyGatedLinAttn {
+  int32_t n_seqs, max_new;
+  const int32_t* cu_tokens; const int32_t* pos0; const int32_t* slot;
+  const void* q; int64_t ldq; const void* k; int64_t ldk; const void* v; int64_t ldv; int32_t in_dtype;
+  const void* a; int64_t ld_a; int32_t a_dtype;
+  int32_t heads, dim, vdim;
+  float tau, q_scale;
+  float* state;
+  void* out; int64_t ld_out; int32_t out_dtype;
+  int64_t rows; float* workspace; int64_t workspace_floats;
+  void* stream;
+} VyGatedLinAttn;
+VY_API int vy_gated_linear_attn(const VyGatedLinAttn* p);
 
 /* ---- latent attention and mixture-of-experts pieces (csrc/latent.cu) ---------------------------------------------------
  * Pair rotation used below: of a vector's first `rot_dims` entries, (2i, 2i + 1) at position p become
- * (u cos a - v sin a, v cos a + u sin a) with a = p * inv_freq[i] (fp32 table [rot_dims / 2], fp32 angle); the rest pass. */
+ * (u cos a - v sin a, v cos a + u sin a) with a = p * inv_freq[i] (fp32 table [rot_dims / 2], fp32 angle); the rest pass.
+ * rot_scale (0 = 1) multiplies both cos and sin (the magnitude correction of frequency-scaled rotations). */
 
 /* Writes the step's latent rows into a paged pool [num_blocks, block_size, pool_row]: x row = [rank latent | rot_dim key part];
  * the latent is RMS-normed (plain weight [rank], eps inside the root), the key part rotated by the token's position, and
@@ -804,6 +841,7 @@ typedef struct VyLatentWrite {
   /* optional: the same rows also written packed, copy[token * ld_copy + ..] (the step's own rows as a product's input) */
   void* copy; int64_t ld_copy; int32_t copy_dtype;
   void* stream;
+  float rot_scale;
 } VyLatentWrite;
 VY_API int vy_latent_kv_write(const VyLatentWrite* p);
 
@@ -819,6 +857,7 @@ typedef struct VyRopeSplit {
   void* pass_out; int64_t ld_pass; int32_t pass_dtype;
   void* rot_out; int64_t ld_rot; int32_t rot_head, rot_col; int32_t rot_dtype;
   void* stream;
+  float rot_scale;
 } VyRopeSplit;
 VY_API int vy_rope_split(const VyRopeSplit* p);
 
@@ -936,7 +975,11 @@ VY_API int vy_depth_mix(const VyDepthMix* p);
 /* Rotates the query and key heads of a packed projection by position and stores the step's keys and values in their pages, one
  * launch: q [rows, heads * dim] is rotated in place; k [rows, kv_heads * dim] is rotated into k_pool and v [rows, kv_heads * vdim]
  * copied into v_pool at each token's page row (pools as in vy_kv_page_write). Entries (2i, 2i + 1), i < rot_dims / 2, of every
- * head turn by pos * inv_freq[i]; the rest pass. q / k / v share a dtype (fp32 for in-place rotation at full precision). */
+ * head turn by pos * inv_freq[i]; the rest pass. q / k / v share a dtype (fp32 for in-place rotation at full precision).
+ * Options (all 0 = the form above): half_layout pairs entry i with entry i + rot_dims / 2 instead of (2i, 2i + 1); rot_scale
+ * multiplies cos and sin; with unit_rms every head of q and k is divided, after the rotation, by sqrt(mean over dim of its squares
+ * + eps); q_scale / k_scale multiply the heads last. Without pools (k_pool null; no block table needed, v ignored) the rotated keys
+ * go to k_out [rows, kv_heads * dim] (row stride ld_k_out, the dtype of k; may be k itself): the form recurrent mixers use. */
 typedef struct VyRopeKvWrite {
   int32_t n_seqs, max_new;
   const int32_t* cu_tokens; const int32_t* pos0;
@@ -946,6 +989,9 @@ typedef struct VyRopeKvWrite {
   const float* inv_freq;
   void* k_pool; void* v_pool; int32_t pool_dtype;
   void* stream;
+  int32_t half_layout, unit_rms;
+  float eps, rot_scale, q_scale, k_scale;
+  void* k_out; int64_t ld_k_out;
 } VyRopeKvWrite;
 VY_API int vy_rope_kv_write(const VyRopeKvWrite* p);
 

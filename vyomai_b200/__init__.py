@@ -19,4 +19,5 @@ from .paged import HybridBatchEngine, HybridCacheManager, HybridSequence  # noqa
 from .models.gelutar import GelutarConfig, GelutarForCausalLM  # noqa: F401
 from .models.zugunex import ZugunexConfig, ZugunexForCausalLM  # noqa: F401
 from .models.vazepel import VazepelConfig, VazepelForCausalLM  # noqa: F401
+from .models.fubinex import FubinexConfig, FubinexForCausalLM  # noqa: F401
 from .registry import load_model, register_model  # noqa: F401

@@ -217,6 +217,8 @@ int vy_abi_sizeof(const char* name) {
   VY_SZ(VyMoeSort);
   VY_SZ(VyMoeGather);
   VY_SZ(VyMoeCombine);
+  VY_SZ(VyPolyNorm);
+  VY_SZ(VyGatedLinAttn);
 #undef VY_SZ
   return -1;
 }

@@ -9,10 +9,12 @@
 
 namespace vy {
 
-// (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = pos * f, all fp32
-__device__ __forceinline__ void rotate_pair(float& u, float& v, int pos, float f) {
+// (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = pos * f, cos and sin times m, all fp32
+__device__ __forceinline__ void rotate_pair(float& u, float& v, int pos, float f, float m) {
   float sn, cs;
   sincosf(static_cast<float>(pos) * f, &sn, &cs);
+  sn *= m;
+  cs *= m;
   const float a = u * cs - v * sn, b = v * cs + u * sn;
   u = a;
   v = b;
@@ -23,7 +25,7 @@ struct LatDev {
   const int* cu; const int* pos0; const int* table; int tw, bs;
   const void* x; long long ldx; int x_dt;
   int rank, rot_dim, rot_dims;
-  const float* inv_freq;
+  const float* inv_freq; float rot_scale;
   const void* w; int w_dt;
   float eps;
   void* pool; long long pool_row; int pool_dt;
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(128) latent_kv_write_kernel(LatDev d) {
       float u = ld_as_float(d.x, d.x_dt, xo + d.rank + 2 * pr);
       const bool has_v = 2 * pr + 1 < d.rot_dim;
       float v = has_v ? ld_as_float(d.x, d.x_dt, xo + d.rank + 2 * pr + 1) : 0.f;
-      if (2 * pr + 1 < d.rot_dims) rotate_pair(u, v, pos, d.inv_freq[pr]);
+      if (2 * pr + 1 < d.rot_dims) rotate_pair(u, v, pos, d.inv_freq[pr], d.rot_scale);
       lat_store(d, po, co, d.rank + 2 * pr, u);
       if (has_v) lat_store(d, po, co, d.rank + 2 * pr + 1, v);
     }
@@ -71,7 +73,7 @@ struct SplitDev {
   const int* cu; const int* pos0;
   const void* x; long long ldx; int x_dt;
   int heads, pass, rot_dim, rot_dims;
-  const float* inv_freq;
+  const float* inv_freq; float rot_scale;
   void* pass_out; long long ld_pass; int pass_dt;
   void* rot_out; long long ld_rot; int rot_head, rot_col, rot_dt;
 };
@@ -101,7 +103,7 @@ __global__ void __launch_bounds__(128) rope_split_kernel(SplitDev d) {
       float u = ld_as_float(d.x, d.x_dt, src);
       const bool has_v = 2 * pr + 1 < d.rot_dim;
       float v = has_v ? ld_as_float(d.x, d.x_dt, src + 1) : 0.f;
-      if (2 * pr + 1 < d.rot_dims) rotate_pair(u, v, pos, d.inv_freq[pr]);
+      if (2 * pr + 1 < d.rot_dims) rotate_pair(u, v, pos, d.inv_freq[pr], d.rot_scale);
       st_from_float(d.rot_out, d.rot_dt, dst, u);
       if (has_v) st_from_float(d.rot_out, d.rot_dt, dst + 1, v);
     }
@@ -367,7 +369,7 @@ extern "C" int vy_latent_kv_write(const VyLatentWrite* p) {
   d.cu = p->cu_tokens; d.pos0 = p->pos0; d.table = p->block_table; d.tw = p->table_width; d.bs = p->block_size;
   d.x = p->x; d.ldx = p->ldx; d.x_dt = p->x_dtype;
   d.rank = p->rank; d.rot_dim = p->rot_dim; d.rot_dims = p->rot_dims;
-  d.inv_freq = p->inv_freq;
+  d.inv_freq = p->inv_freq; d.rot_scale = p->rot_scale == 0.f ? 1.f : p->rot_scale;
   d.w = p->weight; d.w_dt = p->w_dtype; d.eps = p->eps;
   d.pool = p->pool; d.pool_row = p->pool_row; d.pool_dt = p->pool_dtype;
   VY_CHECK_ARG(!p->copy || (dtype_ok(p->copy_dtype) && p->ld_copy >= p->rank + p->rot_dim), "vy_latent_kv_write: bad copy");
@@ -393,7 +395,7 @@ extern "C" int vy_rope_split(const VyRopeSplit* p) {
   d.cu = p->cu_tokens; d.pos0 = p->pos0;
   d.x = p->x; d.ldx = p->ldx; d.x_dt = p->x_dtype;
   d.heads = p->heads; d.pass = p->pass; d.rot_dim = p->rot_dim; d.rot_dims = p->rot_dims;
-  d.inv_freq = p->inv_freq;
+  d.inv_freq = p->inv_freq; d.rot_scale = p->rot_scale == 0.f ? 1.f : p->rot_scale;
   d.pass_out = p->pass > 0 ? p->pass_out : nullptr; d.ld_pass = p->ld_pass; d.pass_dt = p->pass_dtype;
   d.rot_out = p->rot_out; d.ld_rot = p->ld_rot; d.rot_head = p->rot_head; d.rot_col = p->rot_col; d.rot_dt = p->rot_dtype;
   const int gx = p->max_new < 4096 ? p->max_new : 4096;

@@ -217,6 +217,90 @@ __global__ void __launch_bounds__(PB_T) rope_kv_write_kernel(RopeKvDev d) {
   }
 }
 
+// The general form: one warp per (token, head of q or k). Pair layout (adjacent entries, or entry i with entry i + rot_dims / 2), a
+// common factor on cos and sin, an RMS division of the rotated head, a final scale; keys go to their page rows (values copied beside
+// them) or, without pools, to a packed tensor. A lane holds pairs lane, lane + 32, .. and passing entries rot_dims + lane, ..: dim <= 256.
+struct RopeHeadsDev {
+  RopeKvDev b;
+  int half_layout, unit_rms;
+  float eps, rot_scale, q_scale, k_scale;
+  void* k_out; long long ld_k_out;
+};
+
+__global__ void __launch_bounds__(PB_T) rope_heads_kernel(RopeHeadsDev d) {
+  pdl_trigger();
+  pdl_wait();
+  const RopeKvDev& b = d.b;
+  const int s = blockIdx.y;
+  const int base = b.cu[s], n = b.cu[s + 1] - base;
+  const int half = b.rot_dims / 2, rest = b.dim - b.rot_dims;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = PB_T >> 5;
+  for (int i = blockIdx.x; i < n; i += gridDim.x) {
+    const int pos = b.pos0[s] + i;
+    const long long row = base + i;
+    long long prow = 0;
+    if (b.kp) prow = static_cast<long long>(b.table[static_cast<long long>(s) * b.tw + pos / b.bs]) * b.bs + pos % b.bs;
+    for (int unit = warp; unit < b.heads + b.kv_heads; unit += nwarps) {
+      const bool is_q = unit < b.heads;
+      const int h = is_q ? unit : unit - b.heads;
+      const void* src = is_q ? b.q : b.k;
+      const long long so = row * (is_q ? b.ldq : b.ldk) + static_cast<long long>(h) * b.dim;
+      float pu[4], pv[4], ps[8];
+      float ss = 0.f;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int pr = lane + 32 * r;
+        pu[r] = pv[r] = 0.f;
+        if (pr < half) {
+          const int iu = d.half_layout ? pr : 2 * pr, iv = d.half_layout ? pr + half : 2 * pr + 1;
+          const float u = ld_as_float(src, b.in_dt, so + iu), w = ld_as_float(src, b.in_dt, so + iv);
+          float sn, cs;
+          sincosf(static_cast<float>(pos) * b.inv_freq[pr], &sn, &cs);
+          sn *= d.rot_scale;
+          cs *= d.rot_scale;
+          pu[r] = u * cs - w * sn;
+          pv[r] = w * cs + u * sn;
+          ss = fmaf(pu[r], pu[r], ss);
+          ss = fmaf(pv[r], pv[r], ss);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int c = lane + 32 * r;
+        ps[r] = c < rest ? ld_as_float(src, b.in_dt, so + b.rot_dims + c) : 0.f;
+        ss = fmaf(ps[r], ps[r], ss);
+      }
+      float f = is_q ? d.q_scale : d.k_scale;
+      if (d.unit_rms) f /= sqrtf(warp_sum(ss) / static_cast<float>(b.dim) + d.eps);
+      void* dst;
+      long long dof;
+      int dt;
+      if (is_q) { dst = b.q; dof = so; dt = b.in_dt; }
+      else if (b.kp) { dst = b.kp; dof = (prow * b.kv_heads + h) * b.dim; dt = b.pool_dt; }
+      else { dst = d.k_out; dof = row * d.ld_k_out + static_cast<long long>(h) * b.dim; dt = b.in_dt; }
+      __syncwarp();   // in place: every lane has read its entries before any lane writes (pairs are private to a lane, but keep the order explicit)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int pr = lane + 32 * r;
+        if (pr < half) {
+          const int iu = d.half_layout ? pr : 2 * pr, iv = d.half_layout ? pr + half : 2 * pr + 1;
+          st_from_float(dst, dt, dof + iu, pu[r] * f);
+          st_from_float(dst, dt, dof + iv, pv[r] * f);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int c = lane + 32 * r;
+        if (c < rest) st_from_float(dst, dt, dof + b.rot_dims + c, ps[r] * f);
+      }
+    }
+    if (b.vp) {
+      const long long vo = row * b.ldv, vpo = prow * b.kv_heads * b.vdim;
+      for (int c = threadIdx.x; c < b.kv_heads * b.vdim; c += PB_T) st_from_float(b.vp, b.pool_dt, vpo + c, ld_as_float(b.v, b.in_dt, vo + c));
+    }
+  }
+}
+
 }  // namespace vy
 
 #define VY_NEED_DEVICE(name)                                                   \
@@ -323,20 +407,39 @@ extern "C" int vy_rope_kv_write(const VyRopeKvWrite* p) {
   using namespace vy;
   VY_CHECK_ARG(p != nullptr, "vy_rope_kv_write: null params");
   VY_NEED_DEVICE("vy_rope_kv_write");
-  VY_CHECK_ARG(p->n_seqs > 0 && p->n_seqs <= 65535 && p->max_new > 0 && p->cu_tokens && p->pos0 && p->block_table && p->block_size > 0 &&
-                   p->table_width > 0, "vy_rope_kv_write: bad batch");
-  VY_CHECK_ARG(p->heads > 0 && p->kv_heads > 0 && p->dim > 0 && p->vdim > 0 && p->rot_dims >= 0 && p->rot_dims <= p->dim && p->rot_dims % 2 == 0 &&
+  const bool paged = p->k_pool != nullptr;
+  VY_CHECK_ARG(p->n_seqs > 0 && p->n_seqs <= 65535 && p->max_new > 0 && p->cu_tokens && p->pos0, "vy_rope_kv_write: bad batch");
+  VY_CHECK_ARG(!paged || (p->block_table && p->block_size > 0 && p->table_width > 0), "vy_rope_kv_write: pools need a block table");
+  VY_CHECK_ARG(p->heads >= 0 && p->kv_heads >= 0 && p->heads + p->kv_heads > 0 && p->dim > 0 && p->rot_dims >= 0 && p->rot_dims <= p->dim && p->rot_dims % 2 == 0 &&
                    (p->rot_dims == 0 || p->inv_freq), "vy_rope_kv_write: heads %d / %d, dim %d, vdim %d, rotated %d (even, <= dim)", p->heads,
                p->kv_heads, p->dim, p->vdim, p->rot_dims);
-  VY_CHECK_ARG(p->q && p->k && p->v && p->k_pool && p->v_pool && dtype_ok(p->in_dtype) && dtype_ok(p->pool_dtype), "vy_rope_kv_write: bad tensors");
+  VY_CHECK_ARG((p->heads == 0 || p->q) && (p->kv_heads == 0 || p->k) && dtype_ok(p->in_dtype), "vy_rope_kv_write: bad tensors");
+  if (paged) VY_CHECK_ARG(p->v && p->v_pool && p->vdim > 0 && dtype_ok(p->pool_dtype), "vy_rope_kv_write: bad pools");
+  else VY_CHECK_ARG(p->kv_heads == 0 || p->k_out, "vy_rope_kv_write: without pools the rotated keys need k_out");
   RopeKvDev d;
   d.cu = p->cu_tokens; d.pos0 = p->pos0; d.table = p->block_table; d.tw = p->table_width; d.bs = p->block_size;
   d.q = p->q; d.ldq = p->ldq; d.k = p->k; d.ldk = p->ldk; d.v = p->v; d.ldv = p->ldv; d.in_dt = p->in_dtype;
   d.heads = p->heads; d.kv_heads = p->kv_heads; d.dim = p->dim; d.vdim = p->vdim; d.rot_dims = p->rot_dims;
   d.inv_freq = p->inv_freq;
-  d.kp = p->k_pool; d.vp = p->v_pool; d.pool_dt = p->pool_dtype;
+  d.kp = p->k_pool; d.vp = paged ? p->v_pool : nullptr; d.pool_dt = p->pool_dtype;
   const unsigned gx = static_cast<unsigned>(p->max_new < 65535 ? p->max_new : 65535);
-  VY_CUDA_OK(launch_kernel(rope_kv_write_kernel, dim3(gx, p->n_seqs), dim3(PB_T), 0, static_cast<cudaStream_t>(p->stream), d));
+  const bool general = !paged || p->half_layout || p->unit_rms || (p->rot_scale != 0.f && p->rot_scale != 1.f) || (p->q_scale != 0.f && p->q_scale != 1.f) ||
+                       (p->k_scale != 0.f && p->k_scale != 1.f);
+  if (general) {
+    VY_CHECK_ARG(p->dim <= 256, "vy_rope_kv_write: dim %d > 256", p->dim);
+    RopeHeadsDev g;
+    g.b = d;
+    g.half_layout = p->half_layout ? 1 : 0; g.unit_rms = p->unit_rms ? 1 : 0;
+    g.eps = p->eps;
+    g.rot_scale = p->rot_scale == 0.f ? 1.f : p->rot_scale;
+    g.q_scale = p->q_scale == 0.f ? 1.f : p->q_scale;
+    g.k_scale = p->k_scale == 0.f ? 1.f : p->k_scale;
+    g.k_out = p->k_out; g.ld_k_out = p->ld_k_out;
+    VY_CUDA_OK(launch_kernel(rope_heads_kernel, dim3(gx, p->n_seqs), dim3(PB_T), 0, static_cast<cudaStream_t>(p->stream), g));
+  } else {
+    VY_CHECK_ARG(p->heads > 0 && p->kv_heads > 0, "vy_rope_kv_write: heads");
+    VY_CUDA_OK(launch_kernel(rope_kv_write_kernel, dim3(gx, p->n_seqs), dim3(PB_T), 0, static_cast<cudaStream_t>(p->stream), d));
+  }
   VY_LAUNCH_OK();
   count_launch();
   return VY_OK;

@@ -15,7 +15,7 @@ struct NormDev {
   long long rows; int groups, width;
   const int* row_index;
   const void* x; long long ldx; int x_dt;
-  const void* w; int w_dt, w_mode;
+  const void* w; int w_dt, w_mode, w_full;   // w_full: the weight covers the whole row (one entry per element), not one group
   const void* gate; long long ld_gate; int gate_dt, gate_act;
   float eps, coef; int accumulate;
   void* out; long long ld_out; int out_dt;
@@ -41,14 +41,12 @@ __global__ void __launch_bounds__(128) rms_norm_kernel(NormDev d) {
   const float inv = d.coef / sqrtf(ss / static_cast<float>(d.width) + d.eps);
   const long long go = st * d.ld_gate + static_cast<long long>(grp) * d.width;
   const long long oo = tok * d.ld_out + static_cast<long long>(grp) * d.width;
+  const int wo = d.w_full ? grp * d.width : 0;
   for (int c = lane; c < d.width; c += 32) {
     float y = ld_as_float(d.x, d.x_dt, xo + c) * inv;
-    if (d.w_mode == 1) y *= ld_as_float(d.w, d.w_dt, c);
-    else if (d.w_mode == 2) y *= 1.f + ld_as_float(d.w, d.w_dt, c);
-    if (d.gate) {
-      const float g = ld_as_float(d.gate, d.gate_dt, go + c);
-      y *= d.gate_act == VY_UACT_SIGMOID ? sigmoidf_(g) : g;
-    }
+    if (d.w_mode == 1) y *= ld_as_float(d.w, d.w_dt, wo + c);
+    else if (d.w_mode == 2) y *= 1.f + ld_as_float(d.w, d.w_dt, wo + c);
+    if (d.gate) y *= apply_uact(ld_as_float(d.gate, d.gate_dt, go + c), d.gate_act);
     if (d.accumulate) y += ld_as_float(d.out, d.out_dt, oo + c);
     st_from_float(d.out, d.out_dt, oo + c, y);
     if (d.copy) st_from_float(d.copy, d.copy_dt, tok * d.ld_copy + static_cast<long long>(grp) * d.width + c, y);
@@ -104,6 +102,7 @@ __global__ void __launch_bounds__(256) rms_norm_cached_kernel(NormDev d) {
   }
   if (!live) return;
   const float inv = d.coef / sqrtf(ss / static_cast<float>(d.width) + d.eps);
+  const int wo = d.w_full ? grp * d.width : 0;
   if constexpr (VEC) {
     const long long go = st * d.ld_gate + static_cast<long long>(grp) * d.width;
     const long long oo = static_cast<long long>(tok) * d.ld_out + static_cast<long long>(grp) * d.width;
@@ -115,14 +114,13 @@ __global__ void __launch_bounds__(256) rms_norm_cached_kernel(NormDev d) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         y[e] = xv[4 * i + e] * inv;
-        if (d.w_mode == 1) y[e] *= ld_as_float(d.w, d.w_dt, c + e);
-        else if (d.w_mode == 2) y[e] *= 1.f + ld_as_float(d.w, d.w_dt, c + e);
+        if (d.w_mode == 1) y[e] *= ld_as_float(d.w, d.w_dt, wo + c + e);
+        else if (d.w_mode == 2) y[e] *= 1.f + ld_as_float(d.w, d.w_dt, wo + c + e);
       }
       if (d.gate) {
         const float4 g = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(d.gate) + go + c);
-        const bool sg = d.gate_act == VY_UACT_SIGMOID;
-        y[0] *= sg ? sigmoidf_(g.x) : g.x; y[1] *= sg ? sigmoidf_(g.y) : g.y;
-        y[2] *= sg ? sigmoidf_(g.z) : g.z; y[3] *= sg ? sigmoidf_(g.w) : g.w;
+        y[0] *= apply_uact(g.x, d.gate_act); y[1] *= apply_uact(g.y, d.gate_act);
+        y[2] *= apply_uact(g.z, d.gate_act); y[3] *= apply_uact(g.w, d.gate_act);
       }
       if (d.out_dt == VY_F32) {
         float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(d.out) + oo + c);
@@ -153,12 +151,9 @@ __global__ void __launch_bounds__(256) rms_norm_cached_kernel(NormDev d) {
     const int c = lt + i * TPR;
     if (c < d.width) {
       float y = xv[i] * inv;
-      if (d.w_mode == 1) y *= ld_as_float(d.w, d.w_dt, c);
-      else if (d.w_mode == 2) y *= 1.f + ld_as_float(d.w, d.w_dt, c);
-      if (d.gate) {
-        const float g = ld_as_float(d.gate, d.gate_dt, go + c);
-        y *= d.gate_act == VY_UACT_SIGMOID ? sigmoidf_(g) : g;
-      }
+      if (d.w_mode == 1) y *= ld_as_float(d.w, d.w_dt, wo + c);
+      else if (d.w_mode == 2) y *= 1.f + ld_as_float(d.w, d.w_dt, wo + c);
+      if (d.gate) y *= apply_uact(ld_as_float(d.gate, d.gate_dt, go + c), d.gate_act);
       if (d.accumulate) y += ld_as_float(d.out, d.out_dt, oo + c);
       st_from_float(d.out, d.out_dt, oo + c, y);
       if (d.copy) st_from_float(d.copy, d.copy_dt, static_cast<long long>(tok) * d.ld_copy + static_cast<long long>(grp) * d.width + c, y);
@@ -238,8 +233,8 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WinDev d) {
   __syncwarp();
   const int pos = d.pos0[s] + qi;
   // visible keys: [0, nA) (kept first tokens) and [lowB, pos] (the window), disjoint by construction
-  const int nA = d.window <= 0 ? pos + 1 : min(d.keep, pos + 1);
-  const int lowB = d.window <= 0 ? pos + 1 : max(pos - d.window + 1, nA);
+  int nA, lowB;
+  visible_keys(d, pos, nA, lowB);
   const int count = nA + (pos + 1 - lowB);
   float m = -INFINITY, l = 0.f;
   if (d.sink) {
@@ -281,7 +276,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WinDev d) {
       }
     }
   }
-  float og = 1.f / l;
+  float og = d.out_scale / l;
   if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
 #pragma unroll
   for (int r = 0; r < WA_VR; ++r) {
@@ -322,8 +317,8 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
       qreg[hh][r] = col < d.dim ? ld_as_float(d.q, d.q_dt, qrow * d.ldq + static_cast<long long>(h0 + hh) * d.dim + col) * d.scale : 0.f;
     }
   const int pos = d.pos0[s];
-  const int nA = d.window <= 0 ? pos + 1 : min(d.keep, pos + 1);
-  const int lowB = d.window <= 0 ? pos + 1 : max(pos - d.window + 1, nA);
+  int nA, lowB;
+  visible_keys(d, pos, nA, lowB);
   const int count = nA + (pos + 1 - lowB);
   float m[HG], l[HG];
   float acc[HG][WA_VR];
@@ -450,7 +445,7 @@ __global__ void __launch_bounds__(WD_WARPS * 32) window_attn_decode_kernel(WinDe
     wgt[w] = ms[hh * WD_WARPS + w] == -INFINITY ? 0.f : expf(ms[hh * WD_WARPS + w] - M);
     lt = fmaf(ls[hh * WD_WARPS + w], wgt[w], lt);
   }
-  float og = 1.f / lt;
+  float og = d.out_scale / lt;
   if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
 #pragma unroll
   for (int r = 0; r < WA_VR; ++r) {
@@ -600,7 +595,8 @@ __global__ void __launch_bounds__(128) linear_attn_kernel(RecDev d) {
 template <int DP>
 struct DeltaLanes { static constexpr int value = DP >= 32 ? 8 : 4; };
 
-template <int DP>
+// PLAIN: gated linear attention, the same walk without the correction term (u = v): `a` holds the decays (prepared), q is scaled as read
+template <int DP, bool PLAIN>
 __global__ void __launch_bounds__(32 * DeltaLanes<DP>::value) delta_rule_kernel(RecDev d) {
   pdl_trigger();
   pdl_wait();
@@ -621,8 +617,9 @@ __global__ void __launch_bounds__(32 * DeltaLanes<DP>::value) delta_rule_kernel(
   if (n <= 0) return;
   const bool active = j < d.vdim;
   const int gq = h / (d.heads / d.kv_heads);
-  const float neg_rate = -expf(ld_as_float(d.a_log, d.a_log_dt, h));
+  const float neg_rate = PLAIN ? 0.f : -expf(ld_as_float(d.a_log, d.a_log_dt, h));
   const float qscale = 1.f / sqrtf(static_cast<float>(d.dim));
+  const float q_in = PLAIN ? d.q_scale : 1.f;
   float S[NM][4];
   float* sp = d.state + ((static_cast<long long>(d.slot[s]) * d.heads + h) * d.dim) * d.vdim + j;
   const bool carried = d.pos0[s] > 0;
@@ -653,7 +650,7 @@ __global__ void __launch_bounds__(32 * DeltaLanes<DP>::value) delta_rule_kernel(
       const int e = threadIdx.x + u * T, tt = e >> 5, c = static_cast<int>(blockIdx.x) * 32 + (e & 31);
       rv[u] = (tt < nt && c < d.vdim) ? ld_as_float(d.v, d.in_dt, static_cast<long long>(base + t0 + tt) * d.ldv + static_cast<long long>(h) * d.vdim + c) : 0.f;
     }
-    if (threadIdx.x < nt) rb = ld_as_float(d.b, d.b_dt, static_cast<long long>(base + t0 + threadIdx.x) * d.ld_b + h);
+    if (!PLAIN && threadIdx.x < nt) rb = ld_as_float(d.b, d.b_dt, static_cast<long long>(base + t0 + threadIdx.x) * d.ld_b + h);
   };
   fetch(0);
   for (int t0 = 0; t0 < n; t0 += CT) {
@@ -662,15 +659,15 @@ __global__ void __launch_bounds__(32 * DeltaLanes<DP>::value) delta_rule_kernel(
 #pragma unroll
     for (int u = 0; u < NPF; ++u) {
       const int e = threadIdx.x + u * T, tt = e / DP, i = e - tt * DP;
-      qs[tt][i] = rq[u];
+      qs[tt][i] = rq[u] * q_in;
       ks[tt][i] = rk[u];
       gs[tt][i] = ra[u] == -INFINITY ? 1.f : (d.prepared ? ra[u] : expf(neg_rate * softplusf_(ra[u])));
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) vs[threadIdx.x + u * T] = rv[u];
-    if (threadIdx.x < nt) betas[threadIdx.x] = d.prepared ? rb : sigmoidf_(rb);
+    if (!PLAIN && threadIdx.x < nt) betas[threadIdx.x] = d.prepared ? rb : sigmoidf_(rb);
     __syncthreads();
-    for (int tt = d.prepared ? nt : warp; tt < nt; tt += nwarps) {
+    for (int tt = (PLAIN || d.prepared) ? nt : warp; tt < nt; tt += nwarps) {
       float sq = 0.f, sk = 0.f;
       for (int i = lane; i < DP; i += 32) {
         sq = fmaf(qs[tt][i], qs[tt][i], sq);
@@ -696,15 +693,20 @@ __global__ void __launch_bounds__(32 * DeltaLanes<DP>::value) delta_rule_kernel(
         const float4 g4 = *reinterpret_cast<const float4*>(&gs[tt][4 * LANES * m + 4 * part]);
         k4[m] = *reinterpret_cast<const float4*>(&ks[tt][4 * LANES * m + 4 * part]);
         S[m][0] *= g4.x; S[m][1] *= g4.y; S[m][2] *= g4.z; S[m][3] *= g4.w;
-        r0 = fmaf(S[m][0], k4[m].x, r0);
-        r1 = fmaf(S[m][1], k4[m].y, r1);
-        r0 = fmaf(S[m][2], k4[m].z, r0);
-        r1 = fmaf(S[m][3], k4[m].w, r1);
+        if constexpr (!PLAIN) {
+          r0 = fmaf(S[m][0], k4[m].x, r0);
+          r1 = fmaf(S[m][1], k4[m].y, r1);
+          r0 = fmaf(S[m][2], k4[m].z, r0);
+          r1 = fmaf(S[m][3], k4[m].w, r1);
+        }
       }
-      float r = r0 + r1;
+      float u = vj;
+      if constexpr (!PLAIN) {
+        float r = r0 + r1;
 #pragma unroll
-      for (int o = 1; o < LANES; o <<= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-      const float u = betas[tt] * (vj - r);
+        for (int o = 1; o < LANES; o <<= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+        u = betas[tt] * (vj - r);
+      }
       float o0 = 0.f, o1 = 0.f;
 #pragma unroll
       for (int m = 0; m < NM; ++m) {
@@ -780,6 +782,25 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepDev d) {
   }
 }
 
+// gated linear attention's decays, all tokens in parallel: g = sigmoid(a)^(1 / tau) = exp(-softplus(-a) / tau)
+struct GlaPrepDev {
+  long long rows; int width;
+  const void* a; long long ld_a; int a_dt;
+  float inv_tau;
+  float* g;
+};
+
+__global__ void __launch_bounds__(256) gla_prep_kernel(GlaPrepDev d) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = d.rows * d.width;
+  for (long long e = blockIdx.x * 256LL + threadIdx.x; e < total; e += static_cast<long long>(gridDim.x) * 256) {
+    const long long r = e / d.width;
+    const int c = static_cast<int>(e - r * d.width);
+    d.g[e] = expf(-softplusf_(-ld_as_float(d.a, d.a_dt, r * d.ld_a + c)) * d.inv_tau);
+  }
+}
+
 static int pad_dim(int dim) { return dim <= 16 ? 16 : dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : 256; }
 static int col_threads(int vdim) { return vdim <= 32 ? 32 : vdim <= 64 ? 64 : 128; }
 
@@ -803,7 +824,7 @@ extern "C" int vy_rms_norm(const VyRmsNorm* p) {
   d.rows = static_cast<long long>(p->tokens) * p->groups; d.groups = p->groups; d.width = p->width;
   d.row_index = p->row_index;
   d.x = p->x; d.ldx = p->ldx; d.x_dt = p->x_dtype;
-  d.w = p->weight; d.w_dt = p->w_dtype; d.w_mode = p->w_mode;
+  d.w = p->weight; d.w_dt = p->w_dtype; d.w_mode = p->w_mode; d.w_full = p->w_full ? 1 : 0;
   d.gate = p->gate; d.ld_gate = p->ld_gate; d.gate_dt = p->gate_dtype; d.gate_act = p->gate_act;
   d.eps = p->eps; d.coef = p->coef == 0.f ? 1.f : p->coef; d.accumulate = p->accumulate;
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
@@ -879,6 +900,9 @@ extern "C" int vy_window_attn(const VyWinAttn* p) {
                "vy_window_attn: pool row strides smaller than the rows");
   d.heads = p->heads; d.kv_heads = p->kv_heads; d.dim = p->dim; d.vdim = p->vdim;
   d.scale = p->scale; d.window = p->window; d.keep = p->keep_first;
+  VY_CHECK_ARG(p->chunk >= 0 && (p->chunk == 0 || (p->window <= 0 && p->keep_first == 0)), "vy_window_attn: a chunk size goes without a window and kept tokens");
+  d.chunk = p->chunk;
+  d.out_scale = p->out_scale == 0.f ? 1.f : p->out_scale;
   d.sink = p->sink; d.sink_dt = p->sink_dtype;
   d.gate = p->gate; d.ld_gate = p->ld_gate; d.gate_dt = p->gate_dtype;
   d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
@@ -952,13 +976,21 @@ static cudaError_t launch_linear_attn(const RecDev& d, int n_seqs, cudaStream_t 
   const int threads = col_threads(d.vdim);
   return launch_kernel(linear_attn_kernel<DP>, dim3((d.vdim + threads - 1) / threads, d.heads, n_seqs), dim3(threads), 0, st, d);
 }
-template <int DP>
+template <int DP, bool PLAIN = false>
 static cudaError_t launch_delta_rule(const RecDev& d, int n_seqs, cudaStream_t st) {
   const int threads = 32 * DeltaLanes<DP>::value;   // 32 state columns per CTA
   constexpr int CT = RecChunk<DP>::CT;
   const size_t smem = sizeof(float) * (3 * CT * DP + CT + CT * 32);
   const int cols = 32;
-  return launch_kernel(delta_rule_kernel<DP>, dim3((d.vdim + cols - 1) / cols, d.heads, n_seqs), dim3(threads), smem, st, d);
+  if (DP >= 256) {
+    static bool once = false;
+    if (!once) {
+      cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<DP, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+      if (e != cudaSuccess) return e;
+      once = true;
+    }
+  }
+  return launch_kernel(delta_rule_kernel<DP, PLAIN>, dim3((d.vdim + cols - 1) / cols, d.heads, n_seqs), dim3(threads), smem, st, d);
 }
 }  // namespace vy
 
@@ -1047,15 +1079,52 @@ extern "C" int vy_delta_rule(const VyDeltaRule* p) {
     case 32: e = launch_delta_rule<32>(d, p->n_seqs, st); break;
     case 64: e = launch_delta_rule<64>(d, p->n_seqs, st); break;
     case 128: e = launch_delta_rule<128>(d, p->n_seqs, st); break;
-    default: {
-      static bool once = false;
-      if (!once) {
-        cudaFuncSetAttribute(delta_rule_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-        once = true;
-      }
-      e = launch_delta_rule<256>(d, p->n_seqs, st);
-      break;
-    }
+    default: e = launch_delta_rule<256>(d, p->n_seqs, st); break;
+  }
+  VY_CUDA_OK(e);
+  VY_LAUNCH_OK();
+  count_launch();
+  return VY_OK;
+}
+
+extern "C" int vy_gated_linear_attn(const VyGatedLinAttn* p) {
+  using namespace vy;
+  VY_CHECK_ARG(p != nullptr, "vy_gated_linear_attn: null params");
+  VY_NEED_DEVICE("vy_gated_linear_attn");
+  VY_CHECK_ARG(p->n_seqs > 0 && p->n_seqs <= 65535 && p->cu_tokens && p->pos0 && p->slot, "vy_gated_linear_attn: bad batch");
+  VY_CHECK_ARG(p->heads > 0 && p->heads <= 65535 && p->dim > 0 && p->dim <= 256 && p->vdim > 0 && p->tau > 0.f,
+               "vy_gated_linear_attn: heads %d, dim %d (<= 256), vdim %d, tau %g (> 0)", p->heads, p->dim, p->vdim, static_cast<double>(p->tau));
+  VY_CHECK_ARG(p->q && p->k && p->v && p->a && p->state && p->out && dtype_ok(p->in_dtype) && dtype_ok(p->a_dtype) && dtype_ok(p->out_dtype),
+               "vy_gated_linear_attn: bad tensors");
+  const long long width = static_cast<long long>(p->heads) * p->dim;
+  VY_CHECK_ARG(p->rows > 0 && p->workspace && p->workspace_floats >= p->rows * width, "vy_gated_linear_attn: the workspace holds rows * heads * dim floats");
+  cudaStream_t st = static_cast<cudaStream_t>(p->stream);
+  GlaPrepDev pd;
+  pd.rows = p->rows; pd.width = static_cast<int>(width);
+  pd.a = p->a; pd.ld_a = p->ld_a; pd.a_dt = p->a_dtype;
+  pd.inv_tau = 1.f / p->tau;
+  pd.g = p->workspace;
+  const long long blocks = (p->rows * width + 255) / 256;
+  VY_CUDA_OK(launch_kernel(gla_prep_kernel, dim3(static_cast<unsigned>(blocks < 65535 * 16 ? blocks : 65535 * 16)), dim3(256), 0, st, pd));
+  VY_LAUNCH_OK();
+  count_launch();
+  RecDev d;
+  memset(&d, 0, sizeof(d));
+  d.cu = p->cu_tokens; d.pos0 = p->pos0; d.slot = p->slot;
+  d.q = p->q; d.ldq = p->ldq; d.k = p->k; d.ldk = p->ldk; d.v = p->v; d.ldv = p->ldv; d.in_dt = p->in_dtype;
+  d.a = pd.g; d.ld_a = width; d.a_dt = VY_F32;
+  d.heads = p->heads; d.kv_heads = p->heads; d.dim = p->dim; d.vdim = p->vdim;
+  d.prepared = 1;
+  d.q_scale = p->q_scale == 0.f ? 1.f : p->q_scale;
+  d.state = p->state;
+  d.out = p->out; d.ld_out = p->ld_out; d.out_dt = p->out_dtype;
+  cudaError_t e;
+  switch (pad_dim(p->dim)) {
+    case 16: e = launch_delta_rule<16, true>(d, p->n_seqs, st); break;
+    case 32: e = launch_delta_rule<32, true>(d, p->n_seqs, st); break;
+    case 64: e = launch_delta_rule<64, true>(d, p->n_seqs, st); break;
+    case 128: e = launch_delta_rule<128, true>(d, p->n_seqs, st); break;
+    default: e = launch_delta_rule<256, true>(d, p->n_seqs, st); break;
   }
   VY_CUDA_OK(e);
   VY_LAUNCH_OK();

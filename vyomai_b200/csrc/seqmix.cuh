@@ -113,10 +113,19 @@ struct WinDev {
   long long k_row, v_row;   // row strides of the pools in elements (kv_heads * dim and kv_heads * vdim unless the caller views one pool twice)
   int heads, kv_heads, dim, vdim;
   float scale; int window, keep;
+  float out_scale;   // multiplies the normalised output (fp32, before it is rounded to the output dtype)
+  int chunk;   // > 0: keys of the query's own block of `chunk` positions only (window and keep are then 0)
   const void* sink; int sink_dt;
   const void* gate; long long ld_gate; int gate_dt;
   void* out; long long ld_out; int out_dt;
 };
+
+// One query's visible keys at position pos: [0, nA) (kept first tokens) and [lowB, pos] (the window, or the query's chunk), disjoint
+__device__ __forceinline__ void visible_keys(const WinDev& d, int pos, int& nA, int& lowB) {
+  if (d.chunk > 0) { nA = 0; lowB = pos / d.chunk * d.chunk; }
+  else if (d.window <= 0) { nA = pos + 1; lowB = pos + 1; }
+  else { nA = min(d.keep, pos + 1); lowB = max(pos - d.window + 1, nA); }
+}
 
 // recurrences (linear attention with a fixed decay, gated delta rule): state [slots, heads, dim, vdim] fp32
 struct RecDev {
@@ -129,6 +138,7 @@ struct RecDev {
   int heads, kv_heads, dim, vdim;
   float unit_eps;
   int prepared;   // delta rule: q / k are unit vectors already (q scaled), `a` holds the decays and `b` the write strengths
+  float q_scale;  // gated linear attention (the delta kernel without its correction term): multiplies q as it is read
   float* state;
   void* out; long long ld_out; int out_dt;
 };

@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(WT_T, BN == 32 ? 2 : 1) window_attn_tiled_kern
                [&](int i) { return i < rows ? static_cast<long long>(base + i0 + i) * d.ldq + static_cast<long long>(h) * d.dim : -1LL; });
   const int p_lo = d.pos0[s] + i0, p_hi = p_lo + rows - 1;
   // visible keys of the tile's queries: [0, nA) (kept first tokens outside the band) and [lo, p_hi] (the band); masks are per pair
-  const int lo = d.window <= 0 ? 0 : max(p_lo - d.window + 1, 0);
+  const int lo = d.chunk > 0 ? p_lo / d.chunk * d.chunk : d.window <= 0 ? 0 : max(p_lo - d.window + 1, 0);
   const int nA = d.window <= 0 ? 0 : min(d.keep, lo);
   const int count = nA + (p_hi - lo + 1);
   const int* tab = d.table + static_cast<long long>(s) * d.tw;
@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(WT_T, BN == 32 ? 2 : 1) window_attn_tiled_kern
       for (int c = 0; c < NCB; ++c) {
         const int i = ti + 16 * r, j = tj + 16 * c;
         const int p = p_lo + i, kp = kpos_s[j];
-        const bool vis = i < rows && kp >= 0 && kp <= p && (d.window <= 0 || p - kp < d.window || kp < d.keep);
+        const bool vis = i < rows && kp >= 0 && kp <= p && (d.window <= 0 || p - kp < d.window || kp < d.keep) && (d.chunk <= 0 || kp >= p / d.chunk * d.chunk);
         Ps[i * WT_LDP + j] = vis ? sc[r][c] * d.scale : -INFINITY;
       }
     __syncthreads();
@@ -376,7 +376,7 @@ __global__ void __launch_bounds__(WT_T, BN == 32 ? 2 : 1) window_attn_tiled_kern
     const int i = ti + 16 * r;
     if (i >= rows) continue;
     const long long qrow = base + i0 + i;
-    float og = 1.f / l_s[i];
+    float og = d.out_scale / l_s[i];
     if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
 #pragma unroll
     for (int mm = 0; mm < MV; ++mm)
@@ -421,8 +421,8 @@ __global__ void __launch_bounds__(WH_T) window_attn_heads_kernel(WinDev d, int l
   rows_to_smem<WH_T>(Qs, ldk, WH_H, d.dim, dim4, d.q, d.q_dt, qvec, VY_UACT_NONE,
                [&](int i) { return i < nh ? qrow * d.ldq + static_cast<long long>(h0 + i) * d.dim : -1LL; });
   const int pos = d.pos0[s];
-  const int nA = d.window <= 0 ? pos + 1 : min(d.keep, pos + 1);
-  const int lowB = d.window <= 0 ? pos + 1 : max(pos - d.window + 1, nA);
+  int nA, lowB;
+  visible_keys(d, pos, nA, lowB);
   const int count = nA + (pos + 1 - lowB);
   // this split's keys: tiles of WH_K dealt out in contiguous runs
   const int ktiles = (count + WH_K - 1) / WH_K, tper = (ktiles + splits - 1) / splits;
@@ -530,7 +530,7 @@ __global__ void __launch_bounds__(WH_T) window_attn_heads_kernel(WinDev d, int l
     if (hh >= nh) continue;
     const int h = h0 + hh;
     if (splits == 1) {
-      float og = 1.f / l_s[hh];
+      float og = d.out_scale / l_s[hh];
       if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
 #pragma unroll
       for (int cc = 0; cc < WH_VC; ++cc) {
@@ -564,7 +564,7 @@ __global__ void __launch_bounds__(64) window_attn_heads_merge_kernel(WinDev d, i
     const float mk = wp[k * (d.vdim + 2)];
     if (mk != -INFINITY) L = fmaf(wp[k * (d.vdim + 2) + 1], expf(mk - M), L);
   }
-  float og = 1.f / L;
+  float og = d.out_scale / L;
   const long long qrow = base;
   if (d.gate) og *= sigmoidf_(ld_as_float(d.gate, d.gate_dt, qrow * d.ld_gate + h));
   for (int c = threadIdx.x; c < d.vdim; c += blockDim.x) {
@@ -613,7 +613,7 @@ cudaError_t launch_window_attn_heads(const WinDev& d, int n_seqs, float* ws, lon
   }
   const int per_kv = d.heads / d.kv_heads, tiles = (per_kv + WH_H - 1) / WH_H;
   // splits: enough CTAs for two per SM, at most one per 64 keys of the longest possible context, at most 16 and what the workspace holds
-  const long long kmax = d.window > 0 ? static_cast<long long>(d.window) + d.keep : static_cast<long long>(d.tw) * d.bs;
+  const long long kmax = d.chunk > 0 ? d.chunk : d.window > 0 ? static_cast<long long>(d.window) + d.keep : static_cast<long long>(d.tw) * d.bs;
   long long splits = wh_split_bound(n_seqs, d.heads, d.kv_heads);
   splits = splits < (kmax + WH_K - 1) / WH_K ? splits : (kmax + WH_K - 1) / WH_K;
   if (!ws || ws_floats < static_cast<long long>(n_seqs) * d.heads * splits * (d.vdim + 2)) splits = 1;

@@ -1,5 +1,6 @@
-"""Sequence mixers and feed-forwards of the packed-step decoder families (models/gelutar.py, models/zugunex.py, models/vazepel.py),
-on the packed-batch kernels of csrc/seqmix.cu, csrc/latent.cu, csrc/talking_attn.cu and csrc/parallel_block.cu. Each mixer is built from its config block and its weights, declares what it keeps per sequence
+"""Sequence mixers and feed-forwards of the packed-step decoder families (models/gelutar.py, models/zugunex.py, models/vazepel.py,
+models/fubinex.py), on the packed-batch kernels of csrc/seqmix.cu, csrc/latent.cu, csrc/talking_attn.cu, csrc/parallel_block.cu and
+csrc/rowwise.cu. Each mixer is built from its config block and its weights, declares what it keeps per sequence
 (`cache_spec`: pages of keys / values, recurrent state slots) and maps the normed layer input h [rows, width] to its
 output; the constants of a mechanism (window, kept tokens, scale, sink, decay, taps, head counts) are constructor
 arguments, so another architecture can reuse a mixer with other values.
@@ -36,6 +37,8 @@ class Projection:
     def __call__(self, x: torch.Tensor, *, act: Optional[str] = None, bias: Optional[torch.Tensor] = None, scale: float = 1.0,
                  addend: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.float32, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         N = self.out_features
+        if addend is not None and scale != 1.0:   # the two kernels order the scale and the addend differently
+            raise _lib.VyomError("Projection: a scale together with an addend is not defined; fold the scale into the input")
         if out is None:
             out = torch.empty((x.shape[0], _round_up(N, 8)), device=x.device, dtype=out_dtype)[:, :N]
         tc = self.tensor_cores and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 \
@@ -73,10 +76,37 @@ def pack_biases(spans: List[Tuple[int, int]], total: int, biases: List[Optional[
     return out
 
 
+def rotary_frequencies(rot: dict, dims: int, device) -> Tuple[torch.Tensor, float]:
+    """(inv_freq fp32 [dims / 2], factor on cos and sin) of a rotation block {"base", "dims", "scaling"?}. Without scaling
+    f_i = base^(-2i / dims) and the factor is 1. scaling = {"factor", "original", "fast", "slow"} stretches the slow frequencies
+    (YaRN): with n(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), dims - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is f_i / factor where the ramp is 1, f_i where it is 0, their
+    blend between, and cos / sin are multiplied by 0.1 ln(factor) + 1."""
+    import math
+    base = float(rot.get("base", 10000.0))
+    half = dims // 2
+    f = [base ** (-2.0 * i / dims) for i in range(half)] or [0.0]
+    factor_out = 1.0
+    sc = rot.get("scaling")
+    if sc and half:
+        factor, orig = float(sc["factor"]), float(sc["original"])
+        turns = lambda t: dims * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(base))  # noqa: E731
+        lo = max(math.floor(turns(float(sc["fast"]))), 0)
+        hi = min(math.ceil(turns(float(sc["slow"]))), dims - 1)
+        for i in range(half):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp)
+        factor_out = 0.1 * math.log(factor) + 1.0
+    return torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device), factor_out
+
+
 class Mixer:
     """Common surface: `cache_spec()` -> {"pages": (kv_heads, dim, vdim) | None, "states": {name: per-slot shape}};
     `input_weights()` -> the [out, in] matrices that read the layer input (packed by the layer into one projection), `input_biases()` ->
-    their biases (None entries for none); `forward(parts, batch, cache)` with `parts` the list of product blocks in the same order."""
+    their biases (None entries for none); `forward(parts, batch, cache)` with `parts` the list of product blocks in the same order.
+    Mixers that can stand beside another one in a layer also take `x_residual` (the fp32 residual their output projection adds into in
+    its epilogue) and `out_scale` (the mixer's weight in the layer's sum, multiplied in fp32 into what the output projection reads,
+    before that is rounded)."""
 
     def cache_spec(self) -> dict:
         return {"pages": None, "states": {}}
@@ -199,14 +229,129 @@ class GatedDeltaMixer(Mixer):
         return self.o(on)
 
 
+class RetentionMixer(Mixer):
+    """Linear attention with one fixed decay per head and rotated queries / keys, no softmax and no denominator: q, k turn by position
+    (entry i paired with entry i + rot.dims / 2 on the leading rot.dims entries of each head), k is then scaled by dim^-1/2,
+    S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t; each head's read-out is divided by its root mean square (no weight), the heads
+    are gated by silu(W_g h) and projected. The state is fp32 per sequence slot."""
+
+    def __init__(self, cfg: dict, w: Dict[str, torch.Tensor], eps: float, act_dtype: torch.dtype, tensor_cores: bool):
+        self.heads, self.dim, self.vdim = int(cfg["heads"]), int(cfg["dim"]), int(cfg["vdim"])
+        if len(cfg["decay"]) != self.heads:
+            raise ValueError("retention: one decay per head expected")
+        rot = cfg.get("rot") or {}
+        self.rot_dims = int(rot.get("dims", 0))
+        if self.rot_dims > self.dim or self.rot_dims % 2:
+            raise ValueError("retention: rot.dims must be even and at most dim")
+        self.eps, self.act_dtype = eps, act_dtype
+        dev = w["q"].device
+        self.inv_freq, self.rot_scale = rotary_frequencies(rot, self.rot_dims, dev)
+        self.decay = torch.tensor([float(d) for d in cfg["decay"]], dtype=torch.float32, device=dev)
+        self._in = [w["q"], w["k"], w["v"], w["g"]]
+        self.o = Projection(w["o"], tensor_cores)
+
+    def input_weights(self):
+        return self._in
+
+    def cache_spec(self):
+        return {"pages": None, "states": {"S": (self.heads, self.dim, self.vdim)}}
+
+    def forward(self, parts, batch, cache, x_residual: Optional[torch.Tensor] = None, out_scale: float = 1.0):
+        q, k, v, g = parts
+        ops.rope_kv_write(batch, q, k, None, self.inv_freq, None, None, heads=self.heads, kv_heads=self.heads, dim=self.dim, vdim=self.vdim,
+                          rot_dims=self.rot_dims, layout="half", rot_scale=self.rot_scale, k_scale=self.dim ** -0.5, k_out=k)
+        o = ops.linear_attn(batch, q, k, v, self.decay, cache.states["S"], heads=self.heads, dim=self.dim, vdim=self.vdim, in_act=None)
+        og = ops.rms_norm(o, None, eps=self.eps, groups=self.heads, gate=g, gate_act="silu", coef=out_scale, out_dtype=self.act_dtype)
+        return self.o(og, addend=x_residual, out=x_residual)
+
+
+class GatedLinearAttention(Mixer):
+    """Linear attention with a learned decay per key channel and token: q = W_q h dim^-1/2, k = W_k h, v = W_v h,
+    alpha = sigmoid(W_a2 W_a1 h + b_a2)^(1 / tau) (heads x dim), S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t; each head's
+    read-out is RMS-normed with one weight [vdim] shared by the heads, the heads are gated by silu(W_g h) and projected. Decay logits,
+    decays and state are fp32."""
+
+    def __init__(self, cfg: dict, w: Dict[str, torch.Tensor], eps: float, act_dtype: torch.dtype, tensor_cores: bool):
+        self.heads, self.dim, self.vdim = int(cfg["heads"]), int(cfg["dim"]), int(cfg["vdim"])
+        self.tau = float(cfg.get("tau", 1.0))
+        if self.tau <= 0.0:
+            raise ValueError("gated linear attention: tau must be positive")
+        self.eps, self.act_dtype = eps, act_dtype
+        self._in = [w["q"], w["k"], w["v"], w["g"], w["a1"]]
+        self.a2 = Projection(w["a2"], False)   # contraction over the low rank: fp32 activations straight from the a1 block
+        self.a2_bias = w["a2.b"].contiguous()
+        self.norm = w["norm"].contiguous()
+        self.o = Projection(w["o"], tensor_cores)
+
+    def input_weights(self):
+        return self._in
+
+    def cache_spec(self):
+        return {"pages": None, "states": {"S": (self.heads, self.dim, self.vdim)}}
+
+    def forward(self, parts, batch, cache, x_residual: Optional[torch.Tensor] = None, out_scale: float = 1.0):
+        q, k, v, g, a1 = parts
+        a = self.a2(a1, bias=self.a2_bias)
+        o = ops.gated_linear_attn(batch, q, k, v, a, cache.states["S"], heads=self.heads, dim=self.dim, vdim=self.vdim, tau=self.tau,
+                                  q_scale=self.dim ** -0.5)
+        on = ops.rms_norm(o, self.norm, eps=self.eps, w_mode="plain", groups=self.heads, gate=g, gate_act="silu", coef=out_scale, out_dtype=self.act_dtype)
+        return self.o(on, addend=x_residual, out=x_residual)
+
+
+class RotaryAttention(Mixer):
+    """Grouped-query softmax attention with rotated queries / keys over pages: the leading rot.dims entries of each head turn by
+    position (`layout` "half": entry i with entry i + rot.dims / 2; "pairs": entries 2i, 2i + 1), then, with `unit_rms`, every head of q
+    and k is divided by its root mean square over dim (no weight); score = q . k * scale. mask = {"size": n} limits a query to its own
+    block of n consecutive positions counted from position 0 (`mask_kind` "chunk") or to the last n positions ("window"); no mask
+    entry = plain causal. Keys (rotated, normed) and values live in pages."""
+
+    def __init__(self, cfg: dict, w: Dict[str, torch.Tensor], eps: float, act_dtype: torch.dtype, tensor_cores: bool,
+                 kv_dtype: torch.dtype = torch.float32, layout: str = "half", unit_rms: bool = True, mask_kind: str = "chunk"):
+        self.heads, self.kv_heads = int(cfg["heads"]), int(cfg["kv_heads"])
+        self.dim, self.vdim = int(cfg["dim"]), int(cfg["vdim"])
+        if self.heads % self.kv_heads:
+            raise ValueError("attention: heads must be a multiple of kv_heads")
+        rot = cfg.get("rot") or {}
+        self.rot_dims = int(rot.get("dims", 0))
+        if self.rot_dims > self.dim or self.rot_dims % 2:
+            raise ValueError("attention: rot.dims must be even and at most dim")
+        if mask_kind not in ("chunk", "window"):
+            raise ValueError(f"attention: unknown mask kind {mask_kind!r}")
+        size = int((cfg.get("mask") or {}).get("size", 0))
+        self.chunk, self.window = (size, 0) if mask_kind == "chunk" else (0, size)
+        self.scale = float(cfg["scale"])
+        self.layout, self.unit_rms = layout, bool(unit_rms)
+        self.eps, self.act_dtype, self.kv_dtype = eps, act_dtype, kv_dtype
+        self.inv_freq, self.rot_scale = rotary_frequencies(rot, self.rot_dims, w["q"].device)
+        self._in = [w["q"], w["k"], w["v"]]
+        self.o = Projection(w["o"], tensor_cores)
+
+    def input_weights(self):
+        return self._in
+
+    def cache_spec(self):
+        return {"pages": (self.kv_heads, self.dim, self.vdim), "states": {}, "kv_dtype": self.kv_dtype}
+
+    def forward(self, parts, batch, cache, x_residual: Optional[torch.Tensor] = None, out_scale: float = 1.0):
+        q, k, v = parts
+        ops.rope_kv_write(batch, q, k, v, self.inv_freq, cache.k_pool, cache.v_pool, heads=self.heads, kv_heads=self.kv_heads, dim=self.dim,
+                          vdim=self.vdim, rot_dims=self.rot_dims, layout=self.layout, rot_scale=self.rot_scale, unit_rms=self.unit_rms, eps=self.eps)
+        a = ops.window_attn(batch, q, cache.k_pool, cache.v_pool, heads=self.heads, kv_heads=self.kv_heads, dim=self.dim, vdim=self.vdim,
+                            scale=self.scale, window=self.window, keep_first=0, chunk=self.chunk, out_scale=out_scale, out_dtype=self.act_dtype)
+        return self.o(a, addend=x_residual, out=x_residual)
+
+
 class LatentAttention(Mixer):
     """Attention whose keys and values are linear images of a cached low-rank latent: per token the cache holds the RMS-normed
     latent c [rank] and one rotated key part kr [rot_dim] shared by the heads. Head h scores (qn_h . W_uk_h c + qr_h . kr) * scale
     and outputs W_uv_h sum_j p_j c_j, so the kernels never expand keys or values: the unrotated query part is carried into latent
     space once per token (qa_h = W_uk_h^T qn_h) and the attention runs with ONE key/value head over rows [c | kr] (key = the whole
     row, value = its first `rank` entries, both views of one pool), followed by the per-head value expansion. Pair rotation by
-    position on the rotated parts, sliding window, softmax sink and sigmoid output gate as in WindowSinkAttention. A mixer built
-    with `shared_from` owns no down-projection: it reads the pool of the layer it names with its own W_uk / W_uv / queries.
+    position on the rotated parts (optionally with stretched frequencies and a factor on cos / sin: rot.scaling, see
+    rotary_frequencies), sliding window, softmax sink and sigmoid output gate as in WindowSinkAttention, each only when the
+    configuration / the weights hold it (`mask`, `sink`, `g`). Queries come from the layer input directly (weight `q`) or through a
+    latent of their own (weights `dq`, `dq.norm`, `uq`: q = W_uq RMSnorm(W_dq h)). A mixer built with `shared_from` owns no
+    down-projection: it reads the pool of the layer it names with its own W_uk / W_uv / queries.
 
     Whole prompts (every sequence of the step at position 0, bf16 projections) take the expanded form instead: nothing older
     than the step is visible, so the step's own rows [c | kr] (written packed beside the pages) are expanded by ONE tensor-core
@@ -225,16 +370,18 @@ class LatentAttention(Mixer):
         self.window = int((cfg.get("mask") or {}).get("size", 0))
         self.scale = float(cfg["scale"])
         self.eps, self.act_dtype, self.kv_dtype, self.shared_from = eps, act_dtype, kv_dtype, shared_from
-        self.tensor_cores = bool(tensor_cores) and w["q"].dtype == torch.bfloat16
-        dev = w["q"].device
-        base = float(rot.get("base", 10000.0))
-        f = [base ** (-2.0 * i / self.rot_dims) for i in range(self.rot_dims // 2)] or [0.0]
-        self.inv_freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(dev)
+        self.tensor_cores = bool(tensor_cores) and w["uk"].dtype == torch.bfloat16
+        dev = w["uk"].device
+        self.inv_freq, self.rot_scale = rotary_frequencies(rot, self.rot_dims, dev)
         self.row = self.rank + self.rot_dim   # one pool row: [latent | rotated key part]
         if self.row > 256 or self.rank > 256:
             raise ValueError(f"latent attention: kv_rank + rot_dim = {self.row} exceeds the attention kernels' 256 channels per head")
         H, dn, R, dv = self.heads, self.dim, self.rank, self.vdim
-        self._in = [w["q"]] + ([] if shared_from is not None else [w["dkv"]]) + [w["g"]]
+        self.q_latent, self.has_gate = "dq" in w, "g" in w
+        self._in = [w["dq"] if self.q_latent else w["q"]] + ([] if shared_from is not None else [w["dkv"]]) + ([w["g"]] if self.has_gate else [])
+        if self.q_latent:
+            self.dq_norm = w["dq.norm"].contiguous()
+            self.uq = Projection(w["uq"], tensor_cores)
         self.dkv_norm = None if shared_from is not None else w["dkv.norm"].contiguous()
         self.uk_t = w["uk"].view(H, dn, R).transpose(1, 2).contiguous()   # [H, R, dn]: head h maps qn_h to latent space
         self.uv = w["uv"].view(H, dv, R).contiguous()                       # [H, dv, R]
@@ -271,41 +418,45 @@ class LatentAttention(Mixer):
         for h in range(H):
             ops.gemm(x[:, h * x_head:h * x_head + K], w[h], out=out[:, h * out_head:h * out_head + N])
 
-    def forward(self, parts, batch, cache, expanded: Optional[bool] = None):
-        """expanded: force (True) or forbid (False) the whole-prompt form; None = whenever the step allows it."""
+    def forward(self, parts, batch, cache, expanded: Optional[bool] = None, x_residual: Optional[torch.Tensor] = None):
+        """expanded: force (True) or forbid (False) the whole-prompt form; None = whenever the step allows it. x_residual: the fp32
+        residual the output projection adds into (and returns) in its epilogue."""
         rows, H = parts[0].shape[0], self.heads
         whole = self.expand is not None and ((batch.all_start and batch.max_new >= 16) if expanded is None else bool(expanded))
+        q = parts[0]
+        g = parts[-1] if self.has_gate else None
+        if self.q_latent:   # queries through their own latent: q = W_uq RMSnorm(W_dq h)
+            q = self.uq(ops.rms_norm(q, self.dq_norm, eps=self.eps, w_mode="plain", out_dtype=self.act_dtype))
         if self.shared_from is None:
-            q, dkv, g = parts
+            dkv = parts[1]
             # the step's rows packed in step order, kept on the (shared) cache view for the layers that read this layer's rows
             cache.step_rows = torch.empty((rows, self.row), device=q.device, dtype=self.act_dtype) if whole else None
             ops.latent_kv_write(batch, dkv, self.dkv_norm, self.inv_freq, cache.k_pool, rank=self.rank, rot_dim=self.rot_dim,
-                                rot_dims=self.rot_dims, eps=self.eps, copy_out=cache.step_rows)
+                                rot_dims=self.rot_dims, eps=self.eps, copy_out=cache.step_rows, rot_scale=self.rot_scale)
         else:
-            q, g = parts
             whole = whole and getattr(cache, "step_rows", None) is not None and cache.step_rows.shape[0] == rows
         if whole:
             hd = self.dim + self.rot_dim
             kv = self.expand(cache.step_rows)   # fp32 [rows, H (dim + rot_dim) | H vdim]
             ops.rope_split(batch, q, self.inv_freq, heads=H, keep=self.dim, rot_dim=self.rot_dim, rot_dims=self.rot_dims, pass_out=None, rot_out=q,
-                           rot_head=hd, rot_col=self.dim)   # in place: each thread reads its pair before it writes it
+                           rot_head=hd, rot_col=self.dim, rot_scale=self.rot_scale)   # in place: each thread reads its pair before it writes it
             # the buffer as a one-position-per-page pool in step order: position p of sequence s is row cu_tokens[s] + p
             table = (batch.cu_tokens[:-1, None] + torch.arange(batch.max_new, device=q.device, dtype=torch.int32)[None, :]).contiguous()
             flat = ops.PackedBatch(batch.cu_tokens, batch.pos0, batch.slot, batch.max_new, table, 1)
             a = ops.window_attn(flat, q, kv, kv[:, H * hd:], heads=H, kv_heads=H, dim=hd, vdim=self.vdim, scale=self.scale, window=self.window,
                                 keep_first=0, sink=self.sink, gate=g, out_dtype=self.act_dtype, k_row=kv.stride(0), v_row=kv.stride(0))
-            return self.o(a)
+            return self.o(a, addend=x_residual, out=x_residual)
         Q = torch.empty((rows, H * self.row), device=q.device, dtype=torch.float32)
         qn = torch.empty((rows, H * self.dim), device=q.device, dtype=self.act_dtype)
         ops.rope_split(batch, q, self.inv_freq, heads=H, keep=self.dim, rot_dim=self.rot_dim, rot_dims=self.rot_dims, pass_out=qn, rot_out=Q,
-                       rot_head=self.row, rot_col=self.rank)
+                       rot_head=self.row, rot_col=self.rank, rot_scale=self.rot_scale)
         self._per_head(qn, self.uk_t, Q, self.dim, self.row)
         pool = cache.k_pool
         a = ops.window_attn(batch, Q, pool, pool, heads=H, kv_heads=1, dim=self.row, vdim=self.rank, scale=self.scale, window=self.window,
                             keep_first=0, sink=self.sink, gate=g, out_dtype=self.act_dtype, k_row=self.row, v_row=self.row)
         o = torch.empty((rows, H * self.vdim), device=q.device, dtype=self.act_dtype)
         self._per_head(a, self.uv, o, self.rank, self.vdim)
-        return self.o(o)
+        return self.o(o, addend=x_residual, out=x_residual)
 
 
 class TalkingHeadsAttention(Mixer):
@@ -379,6 +530,25 @@ class ReluSquaredMLP(DenseMLP):
 
     def __init__(self, w: Dict[str, torch.Tensor], act_dtype: torch.dtype, tensor_cores: bool):
         super().__init__(w, act_dtype, tensor_cores, act="relu2")
+
+
+class PolyNormMLP:
+    """W_down act(W_up h) with act = a N(z) + b N(z^2) + c N(z^3) + e over each token's hidden vector z (powers element by element,
+    N(u) = u / sqrt(mean(u^2) + eps)); the four numbers are the tensor `act`. The up projection's fp32 result feeds the activation,
+    which is rounded once for the down projection."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], eps: float, act_dtype: torch.dtype, tensor_cores: bool):
+        self.up, self.down = Projection(w["up"], tensor_cores), Projection(w["down"], tensor_cores)
+        self.coef = tuple(float(v) for v in w["act"].to(torch.float32).cpu().tolist())
+        if len(self.coef) != 4:
+            raise ValueError("PolyNorm: the activation holds four numbers")
+        self.eps, self.act_dtype = eps, act_dtype
+
+    def forward(self, h: torch.Tensor, x_residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        u = ops.poly_norm(self.up(h), self.coef, eps=self.eps, out_dtype=self.act_dtype)
+        if x_residual is None:
+            return self.down(u)
+        return self.down(u, addend=x_residual, out=x_residual)
 
 
 class MoEFeedForward:

@@ -931,10 +931,11 @@ def linear_plain(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tenso
 def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, eps: float, w_mode: Optional[str] = "plain", groups: int = 1,
              gate: Optional[torch.Tensor] = None, gate_act: Optional[str] = "sigmoid", coef: float = 1.0, accumulate: bool = False,
              row_index: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-             copy_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+             copy_out: Optional[torch.Tensor] = None, w_full: bool = False) -> torch.Tensor:
     """Grouped RMS norm (fp32 statistics): each row of x is `groups` runs of width x.shape[1] / groups, every run normalised on
-    its own, times the weight (plain or 1 + w, shared by the runs), times an optional (sigmoid) gate, times coef; optionally
-    added into `out`, optionally reading rows x[row_index]. copy_out: a second copy of what `out` (fp32) receives, in its own dtype."""
+    its own, times the weight (plain or 1 + w; shared by the runs, or with w_full one entry per element of the whole row), times an
+    optional gate passed through gate_act (sigmoid, silu, ...; None = the gate itself), times coef; optionally added into `out`,
+    optionally reading rows x[row_index]. copy_out: a second copy of what `out` (fp32) receives, in its own dtype."""
     _need_cuda(x, weight, gate, out, row_index, copy_out)
     _rows2d(x, "rms_norm x")
     tokens = x.shape[0] if row_index is None else row_index.numel()
@@ -943,8 +944,8 @@ def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, eps: float, w_m
     width = x.shape[1] // groups
     if weight is None:
         w_mode = None
-    elif weight.numel() != width or not weight.is_contiguous():
-        raise _lib.VyomError(f"rms_norm: weight has {weight.numel()} elements, expected {width}")
+    elif weight.numel() != (x.shape[1] if w_full else width) or not weight.is_contiguous():
+        raise _lib.VyomError(f"rms_norm: weight has {weight.numel()} elements, expected {x.shape[1] if w_full else width}")
     if out is None:
         if accumulate:
             raise _lib.VyomError("rms_norm: accumulate needs `out`")
@@ -957,7 +958,22 @@ def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], *, eps: float, w_m
               w_mode=W_MODE[w_mode], gate=_ptr(gate), ld_gate=gate.stride(0) if gate is not None else 0,
               gate_dtype=_dt(gate) if gate is not None else 0, gate_act=UACT[gate_act], eps=float(eps), coef=float(coef),
               accumulate=1 if accumulate else 0, out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), copy=_ptr(copy_out),
-              ld_copy=copy_out.stride(0) if copy_out is not None else 0, copy_dtype=_dt(copy_out) if copy_out is not None else 0, stream=_stream())
+              ld_copy=copy_out.stride(0) if copy_out is not None else 0, copy_dtype=_dt(copy_out) if copy_out is not None else 0, stream=_stream(),
+              w_full=1 if w_full else 0)
+    return out
+
+
+def poly_norm(x: torch.Tensor, coef, *, eps: float, out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-wise polynomial of normalised powers (fp32): coef = (a, b, c, e) gives a N(z) + b N(z^2) + c N(z^3) + e with
+    N(u) = u / sqrt(mean(u^2) + eps) over the row and powers taken element by element."""
+    _need_cuda(x, out)
+    _rows2d(x, "poly_norm x")
+    if out is None:
+        out = torch.empty((x.shape[0], _round_up(x.shape[1], 8)), device=x.device, dtype=out_dtype or x.dtype)[:, :x.shape[1]]
+    _rows2d(out, "poly_norm out")
+    a, b, c3, e = (float(v) for v in coef)
+    _lib.call("vy_poly_norm", "VyPolyNorm", rows=x.shape[0], width=x.shape[1], x=x.data_ptr(), ldx=x.stride(0), x_dtype=_dt(x), a=a, b=b, c3=c3, e=e,
+              eps=float(eps), out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream())
     return out
 
 
@@ -996,9 +1012,10 @@ def kv_page_write(batch: PackedBatch, k: torch.Tensor, v: torch.Tensor, k_pool: 
 
 def window_attn(batch: PackedBatch, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *, heads: int, kv_heads: int, dim: int,
                 vdim: int, scale: float, window: int, keep_first: int, sink: Optional[torch.Tensor] = None,
-                gate: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, k_row: int = 0, v_row: int = 0) -> torch.Tensor:
+                gate: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, k_row: int = 0, v_row: int = 0, chunk: int = 0, out_scale: float = 1.0) -> torch.Tensor:
     """Attention of the step's queries over the paged pools (which already hold the step's keys): causal, restricted to the last
-    `window` positions plus the first `keep_first` ones, optional per-head sink in the softmax denominator, optional per-head
+    `window` positions plus the first `keep_first` ones (or, with `chunk`, to the query's own block of `chunk` consecutive positions
+    counted from position 0), optional per-head sink in the softmax denominator, optional per-head
     sigmoid output gate. k_row / v_row: row strides of the pools in elements when they are not kv_heads * dim | vdim (two views of
     one pool)."""
     _need_cuda(q, k_pool, v_pool, sink, gate)
@@ -1012,13 +1029,13 @@ def window_attn(batch: PackedBatch, q: torch.Tensor, k_pool: torch.Tensor, v_poo
               v_pool=v_pool.data_ptr(), pool_dtype=_dt(k_pool), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=float(scale),
               window=int(window), keep_first=int(keep_first), sink=_ptr(sink), sink_dtype=_dt(sink) if sink is not None else 0,
               gate=_ptr(gate), ld_gate=gate.stride(0) if gate is not None else 0, gate_dtype=_dt(gate) if gate is not None else 0,
-              out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), k_row=int(k_row), v_row=int(v_row), stream=_stream(),
+              out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), k_row=int(k_row), v_row=int(v_row), stream=_stream(), chunk=int(chunk), out_scale=float(out_scale),
               **batch._kw(pages=True, slots=False))
     return out
 
 
 def latent_kv_write(batch: PackedBatch, x: torch.Tensor, weight: torch.Tensor, inv_freq: torch.Tensor, pool: torch.Tensor, *, rank: int, rot_dim: int,
-                    rot_dims: int, eps: float, copy_out: Optional[torch.Tensor] = None) -> None:
+                    rot_dims: int, eps: float, copy_out: Optional[torch.Tensor] = None, rot_scale: float = 1.0) -> None:
     """x [rows, rank + rot_dim] -> pool rows [RMS-normed latent * weight | key part rotated by position] at each token's page row;
     copy_out [rows, >= rank + rot_dim]: the same rows also packed in step order."""
     _need_cuda(x, weight, inv_freq, pool, copy_out)
@@ -1029,11 +1046,11 @@ def latent_kv_write(batch: PackedBatch, x: torch.Tensor, weight: torch.Tensor, i
               inv_freq=inv_freq.data_ptr(), weight=weight.data_ptr(), w_dtype=_dt(weight), eps=float(eps), pool=pool.data_ptr(),
               pool_row=pool.shape[-1] * pool.shape[-2] if pool.dim() == 4 else pool.shape[-1], pool_dtype=_dt(pool), copy=_ptr(copy_out),
               ld_copy=copy_out.stride(0) if copy_out is not None else 0, copy_dtype=_dt(copy_out) if copy_out is not None else 0, stream=_stream(),
-              **batch._kw(pages=True, slots=False))
+              rot_scale=float(rot_scale), **batch._kw(pages=True, slots=False))
 
 
 def rope_split(batch: PackedBatch, x: torch.Tensor, inv_freq: torch.Tensor, *, heads: int, keep: int, rot_dim: int, rot_dims: int,
-               pass_out: Optional[torch.Tensor], rot_out: torch.Tensor, rot_head: int, rot_col: int) -> None:
+               pass_out: Optional[torch.Tensor], rot_out: torch.Tensor, rot_head: int, rot_col: int, rot_scale: float = 1.0) -> None:
     """Per head of x [rows, heads * (keep + rot_dim)]: the leading `keep` entries are copied to pass_out [rows, heads * keep], the
     trailing rot_dim ones rotated by position into rot_out[:, h * rot_head + rot_col : .. + rot_dim]."""
     _need_cuda(x, inv_freq, pass_out, rot_out)
@@ -1044,7 +1061,7 @@ def rope_split(batch: PackedBatch, x: torch.Tensor, inv_freq: torch.Tensor, *, h
     _lib.call("vy_rope_split", "VyRopeSplit", x=x.data_ptr(), ldx=x.stride(0), x_dtype=_dt(x), heads=heads, **{"pass": keep}, rot_dim=rot_dim,
               rot_dims=rot_dims, inv_freq=inv_freq.data_ptr(), pass_out=_ptr(pass_out), ld_pass=pass_out.stride(0) if pass_out is not None else 0,
               pass_dtype=_dt(pass_out) if pass_out is not None else 0, rot_out=rot_out.data_ptr(), ld_rot=rot_out.stride(0), rot_head=rot_head,
-              rot_col=rot_col, rot_dtype=_dt(rot_out), stream=_stream(), **batch._kw(slots=False))
+              rot_col=rot_col, rot_dtype=_dt(rot_out), stream=_stream(), rot_scale=float(rot_scale), **batch._kw(slots=False))
 
 
 ROUTE_KIND = {"sigmoid": C["VY_ROUTE_SIGMOID"], "softmax": C["VY_ROUTE_SOFTMAX"]}
@@ -1138,19 +1155,36 @@ def depth_mix(x: torch.Tensor, y1: torch.Tensor, g1: Optional[torch.Tensor], y2:
               **opt(g2, "g2"), mixed=_ptr(mixed), ld_mixed=mixed.stride(0) if mixed is not None else 0, stream=_stream(), **kw)
 
 
-def rope_kv_write(batch: PackedBatch, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: torch.Tensor, k_pool: torch.Tensor,
-                  v_pool: torch.Tensor, *, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int) -> None:
-    """Rotates q in place by position, rotates k into k_pool and copies v into v_pool at each token's page row (one launch)."""
-    _need_cuda(q, k, v, inv_freq, k_pool, v_pool)
-    for t, n in ((q, "q"), (k, "k"), (v, "v")):
-        _rows2d(t, f"rope_kv_write {n}")
-    if not (q.dtype == k.dtype == v.dtype) or k_pool.dtype != v_pool.dtype or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
-        raise _lib.VyomError("rope_kv_write: q / k / v and the two pools must share a dtype each; pools contiguous")
-    if inv_freq.dtype != torch.float32 or inv_freq.numel() < rot_dims // 2 or q.shape[1] < heads * dim or k.shape[1] < kv_heads * dim or v.shape[1] < kv_heads * vdim:
+def rope_kv_write(batch: PackedBatch, q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optional[torch.Tensor], inv_freq: torch.Tensor,
+                  k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], *, heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int,
+                  layout: str = "pairs", rot_scale: float = 1.0, unit_rms: bool = False, eps: float = 0.0, q_scale: float = 1.0, k_scale: float = 1.0,
+                  k_out: Optional[torch.Tensor] = None) -> None:
+    """Rotates q in place by position, rotates k into k_pool and copies v into v_pool at each token's page row (one launch).
+    layout: "pairs" turns entries (2i, 2i + 1), "half" entries (i, i + rot_dims / 2); rot_scale multiplies cos and sin; unit_rms divides
+    every rotated head of q and k by sqrt(mean of its squares + eps); q_scale / k_scale multiply the heads last. Without pools the
+    rotated keys go to k_out [rows, kv_heads * dim] (may be k itself; v is not touched)."""
+    _need_cuda(q, k, v, inv_freq, k_pool, v_pool, k_out)
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (k_out, "k_out")):
+        if t is not None:
+            _rows2d(t, f"rope_kv_write {n}")
+    ins = [t for t in (q, k, v) if t is not None]
+    if any(t.dtype != ins[0].dtype for t in ins) or (k_out is not None and k_out.dtype != k.dtype):
+        raise _lib.VyomError("rope_kv_write: q / k / v (and k_out) must share a dtype")
+    paged = k_pool is not None
+    if paged and (v_pool is None or v is None or k_pool.dtype != v_pool.dtype or not (k_pool.is_contiguous() and v_pool.is_contiguous())):
+        raise _lib.VyomError("rope_kv_write: the two pools share a dtype and are contiguous, and the values come with them")
+    if layout not in ("pairs", "half"):
+        raise _lib.VyomError(f"rope_kv_write: unknown layout {layout!r}")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() < rot_dims // 2 or (q is not None and q.shape[1] < heads * dim) or \
+            (k is not None and k.shape[1] < kv_heads * dim) or (paged and v.shape[1] < kv_heads * vdim):
         raise _lib.VyomError("rope_kv_write: inv_freq fp32 [rot_dims / 2]; q / k / v as wide as their heads")
-    _lib.call("vy_rope_kv_write", "VyRopeKvWrite", q=q.data_ptr(), ldq=q.stride(0), k=k.data_ptr(), ldk=k.stride(0), v=v.data_ptr(), ldv=v.stride(0),
-              in_dtype=_dt(q), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, rot_dims=rot_dims, inv_freq=inv_freq.data_ptr(),
-              k_pool=k_pool.data_ptr(), v_pool=v_pool.data_ptr(), pool_dtype=_dt(k_pool), stream=_stream(), **batch._kw(pages=True, slots=False))
+    _lib.call("vy_rope_kv_write", "VyRopeKvWrite", q=_ptr(q), ldq=q.stride(0) if q is not None else 0, k=_ptr(k), ldk=k.stride(0) if k is not None else 0,
+              v=_ptr(v) if paged else None, ldv=v.stride(0) if paged else 0, in_dtype=_dt(ins[0]), heads=heads if q is not None else 0,
+              kv_heads=kv_heads if k is not None else 0, dim=dim, vdim=vdim, rot_dims=rot_dims, inv_freq=inv_freq.data_ptr(),
+              k_pool=_ptr(k_pool), v_pool=_ptr(v_pool), pool_dtype=_dt(k_pool) if paged else 0, stream=_stream(),
+              half_layout=1 if layout == "half" else 0, unit_rms=1 if unit_rms else 0, eps=float(eps), rot_scale=float(rot_scale), q_scale=float(q_scale),
+              k_scale=float(k_scale), k_out=_ptr(k_out), ld_k_out=k_out.stride(0) if k_out is not None else 0,
+              **batch._kw(pages=paged, slots=False))
 
 
 TALK_FORM = {None: 0, "rows": 1, "tiled": 2}
@@ -1281,4 +1315,23 @@ def delta_rule(batch: PackedBatch, q: torch.Tensor, k: torch.Tensor, v: torch.Te
               in_dtype=_dt(q), a=a.data_ptr(), ld_a=a.stride(0), a_dtype=_dt(a), b=b.data_ptr(), ld_b=b.stride(0), b_dtype=_dt(b),
               a_log=a_log.data_ptr(), a_log_dtype=_dt(a_log), heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, unit_eps=float(unit_eps),
               state=state.data_ptr(), out=out.data_ptr(), ld_out=out.stride(0), out_dtype=_dt(out), stream=_stream(), **batch._kw())
+    return out
+
+
+def gated_linear_attn(batch: PackedBatch, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, state: torch.Tensor, *, heads: int,
+                      dim: int, vdim: int, tau: float, q_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Gated linear attention: S = diag(g) S + k v^T, o = S^T (q q_scale) per head, with the per-channel decay g = sigmoid(a)^(1 / tau)
+    (a [rows, heads * dim]); state [slots, heads, dim, vdim] fp32 carried per sequence."""
+    _need_cuda(q, k, v, a, state)
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (a, "a")):
+        _rows2d(t, f"gated_linear_attn {n}")
+    if state.dtype != torch.float32 or not state.is_contiguous() or not (q.dtype == k.dtype == v.dtype):
+        raise _lib.VyomError("gated_linear_attn: state is contiguous fp32; q / k / v share a dtype")
+    rows = q.shape[0]
+    out = torch.empty((rows, heads * vdim), device=q.device, dtype=out_dtype or torch.float32)
+    ws = torch.empty(rows * heads * dim, device=q.device, dtype=torch.float32)   # the decays of all tokens
+    _lib.call("vy_gated_linear_attn", "VyGatedLinAttn", rows=rows, workspace=ws.data_ptr(), workspace_floats=ws.numel(), q=q.data_ptr(), ldq=q.stride(0),
+              k=k.data_ptr(), ldk=k.stride(0), v=v.data_ptr(), ldv=v.stride(0), in_dtype=_dt(q), a=a.data_ptr(), ld_a=a.stride(0), a_dtype=_dt(a),
+              heads=heads, dim=dim, vdim=vdim, tau=float(tau), q_scale=float(q_scale), state=state.data_ptr(), out=out.data_ptr(), ld_out=out.stride(0),
+              out_dtype=_dt(out), stream=_stream(), **batch._kw())
     return out

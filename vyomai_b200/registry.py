@@ -42,6 +42,11 @@ def _vazepel(path, **kw):
     return VazepelForCausalLM.from_pretrained(path, **kw)
 
 
+def _fubinex(path, **kw):
+    from .models.fubinex import FubinexForCausalLM
+    return FubinexForCausalLM.from_pretrained(path, **kw)
+
+
 def _custom_lm(path, dtype=torch.bfloat16, device=None, **kw):
     """The RMSNorm / SwiGLU / RoPE decoder (models/custom_transformer.py): config.json holds its Config fields, the checkpoint
     its state_dict."""
@@ -58,4 +63,5 @@ def _custom_lm(path, dtype=torch.bfloat16, device=None, **kw):
 register_model("Gelutar", _gelutar)
 register_model("Zugunex", _zugunex)
 register_model("Vazepel", _vazepel)
+register_model("Fubinex", _fubinex)
 register_model("ModelForCausalLM", _custom_lm)
