@@ -157,6 +157,9 @@ class _Layer:
         parts = [P[:, o:o + n] for o, n in self.spans]
         at = 0
         for m, cnt, c, sc in zip(self.mixers, self.counts, caches, self.out_scales):
+            if sc == 0.0:   # a mixer whose weight in the sum is zero: nothing reads its output, and only itself its state
+                at += cnt
+                continue
             if self.kind == "latent_attention":
                 m.forward(parts[at:at + cnt], batch, c, x_residual=x)
             else:
