@@ -1363,6 +1363,168 @@ def run_talking(args):
                       "data": "synthetic", "sizes": res, "gpu_launches_total": int(launches), "gemm_poisoned": int(L.vy_gemm_poisoned()),
                       "clocks": sampler.result(), "l2": "160 MB buffer rewritten between timed prefill iterations"}))
 
+# ------------------------------------------------------------------------------------------------
+# --workload fubinex: the Fubinex decoder (latent attention with a query latent, block-local attention beside gated linear
+# attention, retention, polynomial feed-forward activation) beside the Gelutar hybrid decoder at equal width / depth / vocabulary
+# (both run on HybridBatchEngine's packed step)
+# ------------------------------------------------------------------------------------------------
+FUBINEX_KERNELS = ("rope_heads", "poly_norm", "gla_prep", "rope_kv_write") + LATENT_KERNELS
+
+
+def fubinex_config(width, layers=8, vocab=32768, chunk=512):
+    """A realistic layer stack, repeated: latent attention (64 + 32 query / key and 64 value channels per head, latent rank 192, query
+    latent width / 2), a second latent layer reading the first one's rows, a parallel layer (128-wide heads, 4 query heads per key /
+    value head, blocks of `chunk` positions; gated linear attention with 128 x 128 states), a retention layer (128 x 128 states);
+    feed-forward 4 x width."""
+    H, H2 = width // 64, width // 128
+    rot = {"base": 10000.0, "dims": 32, "scaling": {"factor": 8.0, "original": 2048, "fast": 16.0, "slow": 2.0}}
+    lat = lambda src: {"heads": H, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 192, "q_rank": width // 2, "scale": 96 ** -0.5, "rot": rot,  # noqa: E731
+                       **({} if src is None else {"kv_from": src})}
+    par = {"left": {"heads": H2, "kv_heads": max(H2 // 4, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": chunk},
+                    "rot": {"base": 10000.0, "dims": 64}}, "left_scale": 0.75,
+           "right": {"heads": H2, "dim": 128, "vdim": 128, "tau": 8.0}, "right_scale": 1.25}
+    ret = {"heads": H2, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * i / max(H2 - 1, 1)) for i in range(H2)], "rot": {"base": 10000.0, "dims": 128}}
+    mlp = {"kind": "dense", "ff": 4 * width}
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        if kind == 0:
+            out.append({"type": "latent_attention", "mixer": lat(None), "mlp": mlp})
+        elif kind == 1:
+            out.append({"type": "latent_attention", "mixer": lat(i - 1), "mlp": mlp})
+        elif kind == 2:
+            out.append({"type": "parallel", "mixer": par, "mlp": mlp})
+        else:
+            out.append({"type": "retention", "mixer": ret, "mlp": mlp})
+    return {"architecture": "Fubinex", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6, "groups": 2}, "layers": out}
+
+
+def _roof(table, names, flop=None, byts=None, fp32_tflops=None, hbm=None):
+    """Achieved rate of the kernel families `names` of a CUPTI table against the fp32 FMA rate and / or the measured copy bandwidth."""
+    ms = sum(table.get(k, {}).get("ms", 0.0) for k in names)
+    if not ms:
+        return None
+    r = {"ms": round(ms, 4)}
+    if flop:
+        r.update(gflop=round(flop / 1e9, 2), tflops=round(flop / ms / 1e9, 2), frac_of_fp32_nominal=round(flop / ms / 1e9 / fp32_tflops, 4))
+    if byts:
+        r.update(MB=round(byts / 1e6, 2), frac_of_hbm=round(byts / (ms * 1e-3) / 1e9 / hbm, 4))
+    return r
+
+
+def measure_fubinex(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, decode_steps=64, steps=5, warmup=3):
+    from vyomai_b200 import FubinexConfig, FubinexForCausalLM, GelutarConfig, GelutarForCausalLM
+    hbm, _, _, src = peaks()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    fp32_tflops = sms * 128 * 2 * 1.965e9 / 1e12
+    cfgd = fubinex_config(width)
+    cfg = FubinexConfig(cfgd)
+    model = FubinexForCausalLM(cfg, FubinexForCausalLM.random_weights(cfg, seed=0, low_rank=64), dtype=torch.bfloat16, device=dev)
+    out = {"width": width, "layers": [L["type"] for L in cfgd["layers"]], "vocab": cfg.vocab, "peaks": src, "fp32_tflops_nominal": round(fp32_tflops, 1)}
+    z = _packed_numbers(dev, model, cfg.vocab, batch_prefill, prompt, batch_decode, decode_steps, steps, warmup, kernels=FUBINEX_KERNELS)
+    kinds = [L["type"] for L in cfgd["layers"]]
+    n_lat, n_par, n_ret, n_all = kinds.count("latent_attention"), kinds.count("parallel"), kinds.count("retention"), len(kinds)
+    lat, par, ret = cfgd["layers"][0]["mixer"], cfgd["layers"][2]["mixer"], cfgd["layers"][3]["mixer"]
+    lf, rt = par["left"], par["right"]
+    tokens, C, ff = batch_prefill * prompt, lf["mask"]["size"], 4 * width
+    rf = dict(fp32_tflops=fp32_tflops, hbm=hbm)
+    pk, dk = z["prefill_kernels"], z["decode_kernels_eager"]
+    # prompts. Attention: two contractions per visible (query, key, head) pair; the tiled kernel serves the causal latent layers (expanded
+    # keys: dim + rot_dim and vdim channels) and the block-local layers (mean visible keys (chunk + 1) / 2) alike
+    vis_c = sum(p % C + 1 for p in range(prompt)) / prompt
+    fl_attn = n_lat * tokens * lat["heads"] * (prompt + 1) / 2.0 * (lat["dim"] + lat["rot_dim"] + lat["vdim"]) * 2 + \
+        n_par * tokens * lf["heads"] * vis_c * (lf["dim"] + lf["vdim"]) * 2
+    # recurrences: per (token, head) and state element, gated linear attention does a decay multiply and two multiply-adds (5 flop), the
+    # chunked fixed-decay kernel is counted as in --workload hybrid
+    z["prefill_roofline"] = {
+        "window_attn_tiled": _roof(pk, ("window_attn_tiled",), flop=fl_attn, **rf),
+        "gated_linear_attn (delta_rule kernel, no correction)": _roof(pk, ("delta_rule",), flop=n_par * tokens * rt["heads"] * rt["dim"] * rt["vdim"] * 5, **rf),
+        "linear_attn_chunk": _roof(pk, ("linear_attn_chunk",), flop=n_ret * tokens * ret["heads"] * (2 * ret["dim"] * ret["vdim"] + 32 * (ret["dim"] + ret["vdim"])) * 2, **rf),
+        # row kernels against the copy bandwidth: fp32 in, bf16 out (poly_norm); q / k read and written in fp32, v copied (rotation)
+        "poly_norm": _roof(pk, ("poly_norm",), byts=n_all * tokens * ff * 6, **rf),
+        "rope_heads": _roof(pk, ("rope_heads",), byts=tokens * (n_par * (lf["heads"] + 2 * lf["kv_heads"]) * lf["dim"] + n_ret * 2 * ret["heads"] * ret["dim"]) * 8, **rf),
+        "rms_norm": _roof(pk, ("rms_norm",), byts=tokens * ((2 * n_all) * width * 6 + n_lat * lat["q_rank"] * 6 + (n_par * rt["heads"] * rt["vdim"] + n_ret * ret["heads"] * ret["vdim"]) * 10), **rf),
+    }
+    # single tokens at context `prompt`: attention reads the visible rows once per (sequence, layer); recurrences read and write their state
+    row = lat["kv_rank"] + lat["rot_dim"]
+    vis_d = prompt % C + 1
+    by_attn = batch_decode * (n_lat * (prompt + 1) * row + n_par * vis_d * lf["kv_heads"] * (lf["dim"] + lf["vdim"])) * 4
+    z["decode_roofline"] = {
+        "window_attn (all single-token forms)": _roof(dk, ("window_attn_heads", "window_attn_heads_merge", "window_attn_decode"), byts=by_attn, **rf),
+        "gated_linear_attn": _roof(dk, ("delta_rule",), byts=n_par * batch_decode * rt["heads"] * rt["dim"] * rt["vdim"] * 8, **rf),
+        "linear_attn": _roof(dk, ("linear_attn",), byts=n_ret * batch_decode * ret["heads"] * ret["dim"] * ret["vdim"] * 8, **rf),
+    }
+    step_bytes = 2.0 * sum(t.numel() for t in fubinex_weights(model)) + by_attn + \
+        batch_decode * (n_par * rt["heads"] * rt["dim"] * rt["vdim"] + n_ret * ret["heads"] * ret["dim"] * ret["vdim"]) * 8
+    if z["decode"]["us_per_step_device"]:
+        z["decode"].update(step_algorithmic_MB=round(step_bytes / 1e6, 1),
+                           hbm_frac_device=round(step_bytes / (z["decode"]["us_per_step_device"] * 1e-6) / 1e9 / hbm, 3))
+    out["fubinex"] = z
+    del model
+    torch.cuda.empty_cache()
+    # the closest existing model: fixed-decay linear attention layers and a parallel (windowed softmax + gated delta rule) layer
+    gd = hybrid_config(width)
+    gcfg = GelutarConfig(gd)
+    gmodel = GelutarForCausalLM(gcfg, GelutarForCausalLM.random_weights(gcfg, seed=0, low_rank=64), dtype=torch.bfloat16, device=dev)
+    gz = _packed_numbers(dev, gmodel, gcfg.vocab, batch_prefill, prompt, batch_decode, decode_steps, steps, warmup, kernels=FUBINEX_KERNELS)
+    glin, gpar = gd["layers"][0]["mixer"], gd["layers"][3]["mixer"]
+    gl, gr = gpar["left"], gpar["right"]
+    g_lin = sum(1 for L in gd["layers"] if L["type"] == "lightning")
+    g_par = len(gd["layers"]) - g_lin
+    Wg, K = gl["mask"]["size"], gl["mask"]["keep_first"]
+    vis = sum(min(p + 1, Wg) + (min(K, p + 1 - Wg) if p + 1 > Wg else 0) for p in range(prompt)) / prompt
+    gpk, gdk = gz["prefill_kernels"], gz["decode_kernels_eager"]
+    gz["prefill_roofline"] = {
+        "window_attn_tiled": _roof(gpk, ("window_attn_tiled",), flop=g_par * tokens * gl["heads"] * vis * (gl["dim"] + gl["vdim"]) * 2, **rf),
+        # the delta rule adds the correction's contraction: a decay multiply and three multiply-adds per state element (7 flop)
+        "delta_rule": _roof(gpk, ("delta_rule",), flop=g_par * tokens * gr["heads"] * gr["dim"] * gr["vdim"] * 7, **rf),
+        "linear_attn_chunk": _roof(gpk, ("linear_attn_chunk",), flop=g_lin * tokens * glin["heads"] * (2 * glin["dim"] * glin["vdim"] + 32 * (glin["dim"] + glin["vdim"])) * 2, **rf),
+        "unary (relu^2 between the feed-forward products, fp32 in / bf16 out)": _roof(gpk, ("unary",), byts=len(gd["layers"]) * tokens * ff * 6, **rf),
+    }
+    gz["decode_roofline"] = {
+        "window_attn (all single-token forms)": _roof(gdk, ("window_attn_heads", "window_attn_heads_merge", "window_attn_decode"),
+                                                      byts=g_par * batch_decode * (Wg + K) * gl["kv_heads"] * (gl["dim"] + gl["vdim"]) * 4, **rf),
+        "delta_rule": _roof(gdk, ("delta_rule",), byts=g_par * batch_decode * gr["heads"] * gr["dim"] * gr["vdim"] * 8, **rf),
+        "linear_attn": _roof(gdk, ("linear_attn",), byts=g_lin * batch_decode * glin["heads"] * glin["dim"] * glin["vdim"] * 8, **rf),
+    }
+    out["gelutar"] = gz
+    del gmodel
+    torch.cuda.empty_cache()
+    return out
+
+
+def fubinex_weights(model):
+    """Every weight a Fubinex decode step reads."""
+    seen = []
+    for L in model.layers:
+        seen.append(L.inp.weight)
+        for m in L.mixers:
+            seen += [getattr(m, n).weight for n in ("o", "uq", "a2") if hasattr(m, n)] + [getattr(m, n) for n in ("uk_t", "uv") if hasattr(m, n)]
+        if L.mlp is not None:
+            seen += [L.mlp.up.weight, L.mlp.down.weight]
+    seen.append(model.head.weight)
+    return seen
+
+
+def run_fubinex(args):
+    from vyomai_b200 import _lib
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus != 1:
+        print(json.dumps({"workload": "fubinex", "error": "the Fubinex decoder measurement runs on one GPU"}))
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    L = _lib.lib()
+    sampler = ClockSampler(0)
+    sampler.start()
+    n0 = L.vy_launch_count()
+    res = [_guarded(measure_fubinex, dev, int(w), steps=max(args.steps // 2, 3), warmup=max(args.warmup, 3)) for w in args.hybrid_sizes.split(",")]
+    launches = L.vy_launch_count() - n0
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    print(json.dumps({"workload": "fubinex", "metric": "fubinex_prefill_and_decode_tokens_per_s", "n_gpus": 1, "dtype": "bf16 (fp32 residual / scores / state)",
+                      "data": "synthetic", "sizes": res, "gpu_launches_total": int(launches), "gemm_poisoned": int(L.vy_gemm_poisoned()),
+                      "clocks": sampler.result(), "l2": "160 MB buffer rewritten between timed prefill iterations"}))
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -1371,14 +1533,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="package", choices=["package", "slots", "hybrid", "latent", "talking"],
+    ap.add_argument("--workload", default="package", choices=["package", "slots", "hybrid", "latent", "talking", "fubinex"],
                     help="package: VisionLanguageModel of the reference package (1 image token + 127 text, the headline); "
                          "slots: the notebook-II form (197 image tokens in a 248-token sequence); "
                          "hybrid: prefill / decode throughput of the Gelutar hybrid decoder beside DecoderModel at equal size (1 GPU, "
                          "its own JSON line; not the headline metric); "
                          "latent: the same for the Zugunex latent-attention / mixture-of-experts decoder beside Gelutar at equal size; "
-                         "talking: the same for the Vazepel parallel-layer decoder (score-exchanging attention heads) beside Zugunex")
-    ap.add_argument("--hybrid-sizes", default="1024,2048", help="--workload hybrid / latent / talking: model widths to measure")
+                         "talking: the same for the Vazepel parallel-layer decoder (score-exchanging attention heads) beside Zugunex; "
+                         "fubinex: the same for the Fubinex decoder (latent / block-local / gated-linear / retention mixers) beside Gelutar")
+    ap.add_argument("--hybrid-sizes", default="1024,2048", help="--workload hybrid / latent / talking / fubinex: model widths to measure")
     ap.add_argument("--no-configs-1-2", action="store_true", help="skip the encoder (C1) / ViT (C2) measurements appended at N = 1")
     ap.add_argument("--no-config5", action="store_true", help="skip the PaliGemma-scale prefill + decode measurement appended at N = 1")
     ap.add_argument("--no-slots", action="store_true", help="skip the notebook-II measurement appended at N = 1")
@@ -1399,6 +1562,8 @@ def main():
         run_latent(args)
     elif args.workload == "talking":
         run_talking(args)
+    elif args.workload == "fubinex":
+        run_fubinex(args)
     else:
         run_ours(args)
 
