@@ -1447,10 +1447,16 @@ def measure_fubinex(dev, width, batch_prefill=4, prompt=2048, batch_decode=32, d
     }
     # single tokens at context `prompt`: attention reads the visible rows once per (sequence, layer); recurrences read and write their state
     row = lat["kv_rank"] + lat["rot_dim"]
-    vis_d = prompt % C + 1
-    by_attn = batch_decode * (n_lat * (prompt + 1) * row + n_par * vis_d * lf["kv_heads"] * (lf["dim"] + lf["vdim"])) * 4
+    vis_d = prompt % C + 1   # keys of the decoded token's own block (the first steps after a prompt of a whole number of blocks see very few)
+    by_lat = batch_decode * n_lat * (prompt + 1) * row * 4
+    by_blk = batch_decode * n_par * vis_d * lf["kv_heads"] * (lf["dim"] + lf["vdim"]) * 4
+    by_attn = by_lat + by_blk
     z["decode_roofline"] = {
-        "window_attn (all single-token forms)": _roof(dk, ("window_attn_heads", "window_attn_heads_merge", "window_attn_decode"), byts=by_attn, **rf),
+        # 8 or more heads per latent row: heads-as-rows tiles with the keys split over CTAs, bound by the FMA rate (two contractions over
+        # kv_rank + rot_dim and kv_rank channels per (head, key)), not by the rows' bytes
+        "latent attention (window_attn_heads + merge)": _roof(dk, ("window_attn_heads", "window_attn_heads_merge"), byts=by_lat,
+                                                              flop=n_lat * batch_decode * lat["heads"] * (prompt + 1) * (row + lat["kv_rank"]) * 2, **rf),
+        "block-local attention (window_attn_decode)": _roof(dk, ("window_attn_decode",), byts=by_blk, **rf),
         "gated_linear_attn": _roof(dk, ("delta_rule",), byts=n_par * batch_decode * rt["heads"] * rt["dim"] * rt["vdim"] * 8, **rf),
         "linear_attn": _roof(dk, ("linear_attn",), byts=n_ret * batch_decode * ret["heads"] * ret["dim"] * ret["vdim"] * 8, **rf),
     }
